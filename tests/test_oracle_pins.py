@@ -1,0 +1,85 @@
+"""The CPU oracle against fixtures produced by the reference's own stock
+modules (tests/golden/make_golden.py).  fp32 reference output vs fp64 oracle:
+agreement to fp32 round-off."""
+import os
+
+import numpy as np
+import torch
+
+from oracle import attention_oracle as ao
+from oracle import trimul_oracle as to
+from oracle.inputs import attention_inputs_cpu_case, trimul_inputs_cpu_case
+
+
+def _close(a, b, rtol=2e-5, atol=2e-6):
+    a = torch.as_tensor(a).double()
+    b = torch.as_tensor(b).double()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, (err, ref)
+
+
+def test_attention_oracle_matches_reference_fixture(golden_dir):
+    gold = np.load(os.path.join(golden_dir, "attention_cpu_case.npz"))
+    inp = attention_inputs_cpu_case(seed=0)
+    out, _ = ao.attention_forward(inp["q"], inp["k"], inp["v"], inp["pair_bias"], inp["res_mask"])
+    d_out = 2.0 * out / out.numel()                       # d mean(out^2)
+    res = ao.attention_forward_backward(inp["q"], inp["k"], inp["v"], inp["pair_bias"], inp["res_mask"], d_out)
+    sub = slice(None, None, 4)
+    _close(res["out"][:, sub], gold["out"])
+    assert abs(res["out"].sum().item() - float(gold["out_sum"])) < 1e-3
+    assert abs(out.square().mean().item() - float(gold["loss"])) < 1e-6
+    _close(res["dq"][:, sub], gold["dq"])
+    _close(res["dk"][:, sub], gold["dk"])
+    _close(res["dv"][:, sub], gold["dv"])
+    _close(res["dbias"], gold["dbias"])
+
+
+def test_attention_oracle_fully_masked_rows_are_zero():
+    inp = attention_inputs_cpu_case(seed=3)
+    inp["res_mask"][:, :2] = float("-inf")
+    out, lse = ao.attention_forward(inp["q"], inp["k"], inp["v"], inp["pair_bias"], inp["res_mask"])
+    assert out[:, :2].abs().max().item() == 0.0
+    assert torch.isneginf(lse[:, :2]).all()
+    res = ao.attention_forward_backward(inp["q"], inp["k"], inp["v"], inp["pair_bias"], inp["res_mask"],
+                                        torch.ones_like(out))
+    for key in ("dq", "dk", "dv"):
+        assert res[key][:, :2].abs().max().item() == 0.0
+        assert torch.isfinite(res[key]).all()
+
+
+def test_attention_oracle_analytic_backward_matches_autograd():
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(2, 3, 2, 17, 8, generator=g, dtype=torch.float64).requires_grad_(True) for _ in range(3))
+    b = torch.randn(1, 1, 2, 17, 17, generator=g, dtype=torch.float64).requires_grad_(True)
+    m = torch.zeros(2, 3, 1, 1, 17, dtype=torch.float64)
+    m[..., 12:] = -1e9
+    out, _ = ao.attention_forward(q, k, v, b, m)
+    d_out = torch.randn(out.shape, generator=g, dtype=torch.float64)
+    out.backward(d_out)
+    res = ao.attention_forward_backward(q.detach(), k.detach(), v.detach(), b.detach(), m, d_out)
+    _close(res["dq"], q.grad, 1e-10, 1e-12)
+    _close(res["dk"], k.grad, 1e-10, 1e-12)
+    _close(res["dv"], v.grad, 1e-10, 1e-12)
+    _close(res["dbias"], b.grad, 1e-10, 1e-12)
+
+
+def _trimul_pin(golden_dir, direction):
+    gold = np.load(os.path.join(golden_dir, f"trimul_{direction}_cpu_case.npz"))
+    inp = trimul_inputs_cpu_case(seed=1)
+    out = to.trimul_forward(inp["z"], direction, inp["mask"], inp["weights"])
+    d_out = 2.0 * out / out.numel()
+    res = to.trimul_forward_backward(inp["z"], direction, inp["mask"], inp["weights"], d_out)
+    _close(res["out"], gold["out"], 5e-5, 5e-6)
+    _close(res["dz"], gold["dz"], 1e-4, 1e-9)
+    for name in ("p_in_weight", "g_in_weight", "p_out_weight", "g_out_weight",
+                 "norm_in_weight", "norm_in_bias", "norm_out_weight", "norm_out_bias"):
+        _close(res["d_" + name], gold["d_" + name], 2e-4, 1e-9)
+
+
+def test_trimul_oracle_outgoing_matches_reference_fixture(golden_dir):
+    _trimul_pin(golden_dir, "outgoing")
+
+
+def test_trimul_oracle_incoming_matches_reference_fixture(golden_dir):
+    _trimul_pin(golden_dir, "incoming")
