@@ -1,0 +1,62 @@
+/*
+ * C ABI of libtpf_b200.so - B200 (sm_100a) kernels for the OpenFold3 pair-stack
+ * operators: triangle attention and the triangle multiplicative update.
+ *
+ * Conventions
+ *  - Every function returns 0 on success or a TPF_ERR_* code; the message for the
+ *    last failure on the calling thread is tpf_last_error_string().
+ *  - All pointers are device pointers unless stated otherwise.  Nothing here
+ *    allocates device memory (except where a function says so) or synchronises;
+ *    work is enqueued on `stream` (a cudaStream_t passed as void*).
+ *  - bf16 tensors are 16-byte aligned; extents are int64_t.
+ *  - Kernels never spin forever: a wait that exceeds its time limit records a
+ *    code that tpf_device_status() returns after the stream has been synchronised.
+ *
+ * Each entry point names the reference interface it stands in for
+ * (paths are relative to the reference project's root).
+ */
+#ifndef TPF_B200_H_
+#define TPF_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TPF_OK 0
+#define TPF_ERR_INVALID_ARGUMENT 1
+#define TPF_ERR_UNSUPPORTED 2
+#define TPF_ERR_CUDA 3
+#define TPF_ERR_WORKSPACE 4
+#define TPF_ERR_DEVICE_STATUS 5
+
+/* Library identification ("tpf_b200 <version> sm_100a"). */
+const char* tpf_version(void);
+
+/* Message of the last error raised on this host thread (never NULL). */
+const char* tpf_last_error_string(void);
+
+/* Reads and clears the device status words of the current device (synchronous
+ * small copies).  *status = 0 when every bounded wait completed.
+ * Stands in for the reference's launch checks, which only call
+ * cudaGetLastError (openfold3/core/kernels/turbopairformer/turbopairformer_triangle_forward.cu:1957). */
+int tpf_device_status(int* status);
+
+/* Batched bf16 GEMM  D[b][m][n] = sum_k A[b][m][k] * B[b][n][k], fp32 accumulate.
+ * a_mn / b_mn = 0: operand stored [batch][mn][k] (k contiguous);
+ *             = 1: operand stored [batch][k][mn] (m or n contiguous).
+ * lda/ldb/ldd and the batch strides are in elements.  out_f32 selects fp32 or bf16 D.
+ * k_per_split > 0 runs `batch` K-slices of ONE problem (D[b] holds slice b's partial sum).
+ * Replaces torch.bmm in
+ * openfold3/core/kernels/turbopairformer/turbopairformer_trimul.py:244-249, 357-362. */
+int tpf_bmm_bf16(const void* A, int64_t lda, int64_t batch_stride_a, int a_mn,
+                 const void* B, int64_t ldb, int64_t batch_stride_b, int b_mn,
+                 void* D, int64_t ldd, int64_t batch_stride_d, int out_f32,
+                 int64_t M, int64_t N, int64_t K, int64_t batch, int64_t k_per_split,
+                 int swizzle_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TPF_B200_H_ */

@@ -1,0 +1,43 @@
+// extern "C" surface of libtpf_b200.so (declarations: include/tpf_b200.h).
+#include "../../include/tpf_b200.h"
+#include "tpf_host.cuh"
+
+namespace tpf {
+
+char* last_error_buffer() {
+  static thread_local char buf[512] = "";
+  return buf;
+}
+
+int bmm_status_fetch_and_clear(int* out);
+int bmm_bf16(const void* A, int64_t lda, int64_t bsa, int a_mn, const void* B, int64_t ldb, int64_t bsb, int b_mn,
+             void* D, int64_t ldd, int64_t bsd, int out_f32, int64_t M, int64_t N, int64_t K, int64_t batch,
+             int64_t k_per_split, int swizzle_bytes, cudaStream_t stream);
+
+}  // namespace tpf
+
+extern "C" {
+
+const char* tpf_version(void) { return "tpf_b200 0.1 sm_100a"; }
+
+const char* tpf_last_error_string(void) { return tpf::last_error_buffer(); }
+
+int tpf_device_status(int* status) {
+  TPF_REQUIRE(status != nullptr, TPF_ERR_INVALID_ARGUMENT, "tpf_device_status: status is NULL");
+  int total = 0, v = 0;
+  int rc = tpf::bmm_status_fetch_and_clear(&v);
+  if (rc) return rc;
+  total |= v;
+  *status = total;
+  return TPF_OK;
+}
+
+int tpf_bmm_bf16(const void* A, int64_t lda, int64_t batch_stride_a, int a_mn, const void* B, int64_t ldb,
+                 int64_t batch_stride_b, int b_mn, void* D, int64_t ldd, int64_t batch_stride_d, int out_f32,
+                 int64_t M, int64_t N, int64_t K, int64_t batch, int64_t k_per_split, int swizzle_bytes,
+                 void* stream) {
+  return tpf::bmm_bf16(A, lda, batch_stride_a, a_mn, B, ldb, batch_stride_b, b_mn, D, ldd, batch_stride_d, out_f32,
+                       M, N, K, batch, k_per_split, swizzle_bytes, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

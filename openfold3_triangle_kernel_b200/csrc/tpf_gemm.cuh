@@ -1,0 +1,270 @@
+// Persistent, warp-specialised tcgen05 GEMM engine for sm_100a.
+//
+//   D[b][m][n] = sum_k A[b][m][k] * B[b][n][k]        (bf16 x bf16 -> fp32 in TMEM)
+//
+// One CTA per SM walks a static list of (batch, m-tile, n-tile) output tiles.
+//   warp 0      : TMA producer  (one elected lane) - STAGES-deep smem ring
+//   warp 1      : UMMA issuer   (one elected lane) - accumulators double-buffered in TMEM
+//   warps 2..5  : epilogue      (128 threads = 128 TMEM lanes = 128 rows of the tile)
+// Either operand may be K-major (k contiguous in memory) or MN-major (m / n
+// contiguous); the shared-memory tiles are written by TMA in the swizzled
+// canonical layouts the UMMA descriptors describe, so no thread touches them.
+//
+// The epilogue is a functor; the TriMul stages plug their fused epilogues in.
+#pragma once
+
+#include "tpf_ptx.cuh"
+
+namespace tpf {
+
+struct GemmShape {
+  int M, N, K;
+  int batch;        // number of independent problems, or number of K splits
+  int k_per_split;  // 0: `batch` indexes the tensors' outer dim; >0: split-K, tile b covers
+                    // k in [b*k_per_split, (b+1)*k_per_split) of ONE problem
+};
+
+template <int BM_, int BN_, int SWZ_A_, bool A_MN_, int SWZ_B_, bool B_MN_, int STAGES_>
+struct GemmCfg {
+  static constexpr int BM = BM_, BN = BN_, SWZ_A = SWZ_A_, SWZ_B = SWZ_B_, STAGES = STAGES_;
+  static constexpr bool A_MN = A_MN_, B_MN = B_MN_;
+  static constexpr int BK_A = A_MN ? 64 : SWZ_A / 2;
+  static constexpr int BK_B = B_MN ? 64 : SWZ_B / 2;
+  static constexpr int BK = BK_A < BK_B ? BK_A : BK_B;  // k elements per pipeline stage
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int CHUNK_A = SWZ_A / 2;  // MN-major: elements per swizzle row
+  static constexpr int CHUNK_B = SWZ_B / 2;
+  static constexpr int TMEM_COLS = 2 * BN;   // two accumulators
+  static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 256 + 1024;
+  static_assert(BM == 128, "UMMA tile M is 128 (one TMEM lane per row)");
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
+  static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
+                "TMEM allocation must be a power of two >= 32");
+  static_assert(A_BYTES % 1024 == 0 && B_BYTES % 1024 == 0, "stage buffers keep 1024-byte alignment");
+};
+
+// Plain stores.  OutT = __nv_bfloat16 or float; row-major D[b][m][n] with leading dimension ldd.
+template <typename OutT>
+struct EpiStore {
+  struct Params {
+    OutT* D;
+    int64_t ldd;
+    int64_t batch_stride;
+  };
+  static constexpr bool kPaired = false;
+  __device__ static __forceinline__ void apply(const Params& p, const GemmShape& sh, int b, int m, int n0,
+                                               const float (&v)[32]) {
+    if (m >= sh.M) return;
+    OutT* row = p.D + (int64_t)b * p.batch_stride + (int64_t)m * p.ldd + n0;
+    if (n0 + 32 <= sh.N && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
+      if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 u;
+          u.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+          u.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+          u.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+          u.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+          reinterpret_cast<uint4*>(row)[i] = u;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          reinterpret_cast<float4*>(row)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < sh.N) row[i] = static_cast<OutT>(v[i]);
+    }
+  }
+};
+
+template <class Cfg, class Epi>
+__global__ void __launch_bounds__(192, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmShape sh, const typename Epi::Params ep, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + Cfg::STAGES * Cfg::A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES));
+  uint64_t* empty = full + Cfg::STAGES;
+  uint64_t* tfull = empty + Cfg::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wctx{abort_flag, status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int mt = (sh.M + Cfg::BM - 1) / Cfg::BM;
+  const int nt = (sh.N + Cfg::BN - 1) / Cfg::BN;
+  const int tiles = sh.batch * mt * nt;
+  const int k_len = sh.k_per_split > 0 ? sh.k_per_split : sh.K;
+  const int kb_count = (k_len + Cfg::BK - 1) / Cfg::BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 1;
+      for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int b = t / (mt * nt);
+        const int r = t - b * (mt * nt);
+        const int m0 = (r / nt) * Cfg::BM;
+        const int n0 = (r % nt) * Cfg::BN;
+        const int kbase = sh.k_per_split > 0 ? b * sh.k_per_split : 0;
+        const int bc = sh.k_per_split > 0 ? 0 : b;
+        for (int kb = 0; kb < kb_count; ++kb) {
+          mbar_wait(&empty[s], ph, wctx);
+          mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
+          const int k0 = kbase + kb * Cfg::BK;
+          uint8_t* a_dst = sA + s * Cfg::A_BYTES;
+          uint8_t* b_dst = sB + s * Cfg::B_BYTES;
+          if constexpr (!Cfg::A_MN) {
+            tma_load_3d(a_dst, &tmA, &full[s], k0, m0, bc);
+          } else {
+#pragma unroll
+            for (int c = 0; c < Cfg::BM / Cfg::CHUNK_A; ++c)
+              tma_load_3d(a_dst + c * Cfg::BK * Cfg::SWZ_A, &tmA, &full[s], m0 + c * Cfg::CHUNK_A, k0, bc);
+          }
+          if constexpr (!Cfg::B_MN) {
+            tma_load_3d(b_dst, &tmB, &full[s], k0, n0, bc);
+          } else {
+#pragma unroll
+            for (int c = 0; c < Cfg::BN / Cfg::CHUNK_B; ++c)
+              tma_load_3d(b_dst + c * Cfg::BK * Cfg::SWZ_B, &tmB, &full[s], n0 + c * Cfg::CHUNK_B, k0, bc);
+          }
+          if (++s == Cfg::STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(Cfg::BM, Cfg::BN, Cfg::A_MN, Cfg::B_MN);
+      constexpr uint32_t sw_a = swizzle_mode_for_bytes(Cfg::SWZ_A);
+      constexpr uint32_t sw_b = swizzle_mode_for_bytes(Cfg::SWZ_B);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 1;
+      for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+        mbar_wait(&tempty[acc], acc_ph, wctx);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * Cfg::BN;
+        for (int kb = 0; kb < kb_count; ++kb) {
+          mbar_wait(&full[s], ph, wctx);
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * Cfg::A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * Cfg::B_BYTES);
+#pragma unroll
+          for (int j = 0; j < Cfg::BK / 16; ++j) {
+            const uint64_t ad = Cfg::A_MN ? make_smem_desc(a_addr + j * 16 * Cfg::SWZ_A, Cfg::BK * Cfg::SWZ_A,
+                                                           8 * Cfg::SWZ_A, sw_a)
+                                          : make_smem_desc(a_addr + j * 32, 16, 8 * Cfg::SWZ_A, sw_a);
+            const uint64_t bd = Cfg::B_MN ? make_smem_desc(b_addr + j * 16 * Cfg::SWZ_B, Cfg::BK * Cfg::SWZ_B,
+                                                           8 * Cfg::SWZ_B, sw_b)
+                                          : make_smem_desc(b_addr + j * 32, 16, 8 * Cfg::SWZ_B, sw_b);
+            umma_ss(d_tmem, ad, bd, idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (++s == Cfg::STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        umma_commit(&tfull[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_ph ^= 1;
+        }
+      }
+    }
+  } else {
+    const int lane_base = 32 * (warp & 3);
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+      const int b = t / (mt * nt);
+      const int r = t - b * (mt * nt);
+      const int m0 = (r / nt) * Cfg::BM;
+      const int n0 = (r % nt) * Cfg::BN;
+      mbar_wait(&tfull[acc], acc_ph, wctx);
+      tc_fence_after();
+      const uint32_t t_acc = tmem_addr(tmem_base, lane_base, acc * Cfg::BN);
+      const int m = m0 + lane_base + lane;
+      if constexpr (!Epi::kPaired) {
+#pragma unroll 1
+        for (int c = 0; c < Cfg::BN; c += 32) {
+          uint32_t raw[32];
+          float v[32];
+          tmem_ld32(t_acc + c, raw);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+          if (n0 + c < sh.N) Epi::apply(ep, sh, b, m, n0 + c, v);
+        }
+      } else {
+        // Column c (first half of the tile) pairs with column c + BN/2.
+#pragma unroll 1
+        for (int c = 0; c < Cfg::BN / 2; c += 32) {
+          uint32_t raw0[32], raw1[32];
+          float v0[32], v1[32];
+          tmem_ld32(t_acc + c, raw0);
+          tmem_ld32(t_acc + Cfg::BN / 2 + c, raw1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v0[i] = __uint_as_float(raw0[i]);
+            v1[i] = __uint_as_float(raw1[i]);
+          }
+          Epi::apply2(ep, sh, b, m, n0, c, v0, v1);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_ph ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace tpf

@@ -1,0 +1,100 @@
+// Host-side helpers shared by the translation units of the C-ABI library:
+// error reporting, TMA descriptor encoding (driver entry point resolved at run
+// time, so the library loads on machines without a CUDA driver), launch checks.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/tpf_b200.h"  // TPF_OK / TPF_ERR_* codes
+
+namespace tpf {
+
+
+char* last_error_buffer();  // thread-local, 512 bytes (defined in tpf_cabi.cu)
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define TPF_REQUIRE(cond, code, ...)                  \
+  do {                                                \
+    if (!(cond)) return ::tpf::fail(code, __VA_ARGS__); \
+  } while (0)
+
+#define TPF_CUDA_OK(expr)                                                                             \
+  do {                                                                                                \
+    cudaError_t _e = (expr);                                                                          \
+    if (_e != cudaSuccess)                                                                            \
+      return ::tpf::fail(TPF_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                         __FILE__, __LINE__);                                                         \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+inline CUtensorMapSwizzle swizzle_enum(int bytes) {
+  return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                      : bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                    : bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+}
+
+// Encode a tiled bf16 tensor map of rank `rank` (2..5).  dims[0] is the
+// contiguous dimension; strides_bytes[i] is the byte stride of dims[i+1].
+inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  TPF_REQUIRE(fn != nullptr, TPF_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+  TPF_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, TPF_ERR_INVALID_ARGUMENT,
+              "tensor base address must be 16-byte aligned");
+  cuuint64_t d[5];
+  cuuint64_t s[4];
+  cuuint32_t b[5], e[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    e[i] = 1;
+    if (i + 1 < rank) {
+      s[i] = strides_bytes[i];
+      TPF_REQUIRE((s[i] & 15) == 0, TPF_ERR_INVALID_ARGUMENT, "tensor stride %d (%llu bytes) must be a multiple of 16",
+                  i + 1, (unsigned long long)s[i]);
+    }
+  }
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum(swizzle_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TPF_REQUIRE(r == CUDA_SUCCESS, TPF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TPF_OK;
+}
+
+inline int sm_count() {
+  static int n = 0;
+  if (n) return n;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  return n;
+}
+
+}  // namespace tpf
