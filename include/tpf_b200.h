@@ -56,6 +56,22 @@ int tpf_bmm_bf16(const void* A, int64_t lda, int64_t batch_stride_a, int a_mn,
                  int64_t M, int64_t N, int64_t K, int64_t batch, int64_t k_per_split,
                  int swizzle_bytes, void* stream);
 
+/* Triangle-attention forward.
+ *   q,k,v   bf16, logical shape [B,O,H,N,D]; *_strides = element strides of (b,o,h,n); the last
+ *           dimension is contiguous (covers both the head-major and the sequence-major storage
+ *           order of the reference).  D in {16,32,64}.  Q is NOT pre-scaled; `scale` multiplies Q K^T.
+ *   mask    fp32 additive [B,O,mask_pitch] (first N entries of each row are used; 0 keeps, -inf drops)
+ *   bias    bf16 [bias_batch,H,N,bias_pitch], bias_batch = 1 (shared by all b) or B
+ *   out     bf16 [B,O,N,H,D] contiguous;  lse fp32 [B,O,H,N] (natural log; -inf for a fully masked row)
+ * Replaces turbopairformer_triangle_forward_out / _forward_shadow_out
+ * (openfold3/core/kernels/turbopairformer/turbopairformer_triangle_forward.cu:1826-2004). */
+int tpf_attn_fwd(const void* q, const void* k, const void* v,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const float* mask, int64_t mask_pitch,
+                 const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                 void* out, float* lse,
+                 int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

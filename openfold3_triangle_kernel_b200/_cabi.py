@@ -16,6 +16,7 @@ _P = ctypes.c_void_p
 _I = ctypes.c_int64
 _i = ctypes.c_int
 _f = ctypes.c_float
+_PI = ctypes.POINTER(ctypes.c_int64)
 
 # name -> argtypes; every function returns int (0 = ok) unless listed in _RESTYPES.
 SIGNATURES = {
@@ -23,6 +24,7 @@ SIGNATURES = {
     "tpf_last_error_string": [],
     "tpf_device_status": [ctypes.POINTER(ctypes.c_int)],
     "tpf_bmm_bf16": [_P, _I, _I, _i, _P, _I, _I, _i, _P, _I, _I, _i, _I, _I, _I, _I, _I, _i, _P],
+    "tpf_attn_fwd": [_P, _P, _P, _PI, _PI, _PI, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _f, _P],
 }
 _RESTYPES = {"tpf_version": ctypes.c_char_p, "tpf_last_error_string": ctypes.c_char_p}
 
@@ -85,6 +87,10 @@ def version():
 
 def ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def i64_array(values):
+    return (ctypes.c_int64 * len(values))(*[int(v) for v in values])
 
 
 def current_stream():

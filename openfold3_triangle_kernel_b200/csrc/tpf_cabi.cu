@@ -14,6 +14,12 @@ int bmm_bf16(const void* A, int64_t lda, int64_t bsa, int a_mn, const void* B, i
              void* D, int64_t ldd, int64_t bsd, int out_f32, int64_t M, int64_t N, int64_t K, int64_t batch,
              int64_t k_per_split, int swizzle_bytes, cudaStream_t stream);
 
+int attn_fwd_status_fetch_and_clear(int* out);
+int attn_fwd(const void* q, const void* k, const void* v, const int64_t* q_strides, const int64_t* k_strides,
+             const int64_t* v_strides, const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch,
+             int64_t bias_batch, void* out, float* lse, int64_t B, int64_t O, int64_t H, int64_t N, int64_t D,
+             float scale, cudaStream_t stream);
+
 }  // namespace tpf
 
 extern "C" {
@@ -28,6 +34,8 @@ int tpf_device_status(int* status) {
   int rc = tpf::bmm_status_fetch_and_clear(&v);
   if (rc) return rc;
   total |= v;
+  if ((rc = tpf::attn_fwd_status_fetch_and_clear(&v))) return rc;
+  total |= v;
   *status = total;
   return TPF_OK;
 }
@@ -38,6 +46,15 @@ int tpf_bmm_bf16(const void* A, int64_t lda, int64_t batch_stride_a, int a_mn, c
                  void* stream) {
   return tpf::bmm_bf16(A, lda, batch_stride_a, a_mn, B, ldb, batch_stride_b, b_mn, D, ldd, batch_stride_d, out_f32,
                        M, N, K, batch, k_per_split, swizzle_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int tpf_attn_fwd(const void* q, const void* k, const void* v, const int64_t* q_strides, const int64_t* k_strides,
+                 const int64_t* v_strides, const float* mask, int64_t mask_pitch, const void* bias,
+                 int64_t bias_pitch, int64_t bias_batch, void* out, float* lse, int64_t B, int64_t O, int64_t H,
+                 int64_t N, int64_t D, float scale, void* stream) {
+  TPF_REQUIRE(q_strides && k_strides && v_strides, TPF_ERR_INVALID_ARGUMENT, "tpf_attn_fwd: stride arrays are NULL");
+  return tpf::attn_fwd(q, k, v, q_strides, k_strides, v_strides, mask, mask_pitch, bias, bias_pitch, bias_batch, out,
+                       lse, B, O, H, N, D, scale, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -60,10 +60,10 @@ inline CUtensorMapSwizzle swizzle_enum(int bytes) {
                                     : bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
 }
 
-// Encode a tiled bf16 tensor map of rank `rank` (2..5).  dims[0] is the
+// Encode a tiled tensor map of rank `rank` (2..5).  dims[0] is the
 // contiguous dimension; strides_bytes[i] is the byte stride of dims[i+1].
-inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                          const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
+inline int make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
   EncodeTiledFn fn = encode_tiled_fn();
   TPF_REQUIRE(fn != nullptr, TPF_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
   TPF_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, TPF_ERR_INVALID_ARGUMENT,
@@ -81,11 +81,20 @@ inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const ui
                   i + 1, (unsigned long long)s[i]);
     }
   }
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
+  CUresult r = fn(out, dtype, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_enum(swizzle_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TPF_REQUIRE(r == CUDA_SUCCESS, TPF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return TPF_OK;
+}
+
+inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
+  return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box, swizzle_bytes);
+}
+inline int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                         const uint64_t* strides_bytes, const uint32_t* box) {
+  return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes, box, 0);
 }
 
 inline int sm_count() {
