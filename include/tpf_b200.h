@@ -72,6 +72,29 @@ int tpf_attn_fwd(const void* q, const void* k, const void* v,
                  void* out, float* lse,
                  int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, void* stream);
 
+/* Bytes of device scratch tpf_attn_bwd needs for this shape (0 is possible). */
+int64_t tpf_attn_bwd_workspace_bytes(int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, int64_t bias_batch);
+
+/* Triangle-attention backward: dq, dk, dv (bf16, contiguous [B,O,H,N,D]), dbias (fp32
+ * [bias_batch,H,N,N], summed over the outer axis and over b when bias_batch == 1) and
+ * delta (fp32 [B,O,H,N], rowsum(dO * O), caller-allocated scratch that is also an output).
+ *   d_out, out   bf16 [B,O,N,H,D] contiguous (gradient of / the forward output)
+ *   lse          fp32 [B,O,H,N] from tpf_attn_fwd
+ *   workspace    at least tpf_attn_bwd_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when 0)
+ * Other arguments as in tpf_attn_fwd.  Deterministic: fixed summation orders, no atomics.
+ * Replaces turbopairformer_triangle_delta_out + turbopairformer_triangle_sr_backward_out
+ * (openfold3/core/kernels/turbopairformer/turbopairformer_triangle_delta.cu:343-414,
+ *  openfold3/core/kernels/turbopairformer/turbopairformer_triangle_dq_dbias.cu:2526-2648) and the
+ * Python workspace planner in turbopairformer_triangle_dq_dbias.py:466-669. */
+int tpf_attn_bwd(const void* q, const void* k, const void* v, const void* d_out,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const void* out, const float* lse,
+                 const float* mask, int64_t mask_pitch,
+                 const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                 void* dq, void* dk, void* dv, float* dbias, float* delta,
+                 void* workspace, int64_t workspace_bytes,
+                 int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

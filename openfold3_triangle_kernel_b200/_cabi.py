@@ -25,8 +25,11 @@ SIGNATURES = {
     "tpf_device_status": [ctypes.POINTER(ctypes.c_int)],
     "tpf_bmm_bf16": [_P, _I, _I, _i, _P, _I, _I, _i, _P, _I, _I, _i, _I, _I, _I, _I, _I, _i, _P],
     "tpf_attn_fwd": [_P, _P, _P, _PI, _PI, _PI, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _f, _P],
+    "tpf_attn_bwd_workspace_bytes": [_I, _I, _I, _I, _I, _I],
+    "tpf_attn_bwd": [_P, _P, _P, _P, _PI, _PI, _PI, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I,
+                     _I, _I, _I, _I, _I, _f, _P],
 }
-_RESTYPES = {"tpf_version": ctypes.c_char_p, "tpf_last_error_string": ctypes.c_char_p}
+_RESTYPES = {"tpf_attn_bwd_workspace_bytes": ctypes.c_int64, "tpf_version": ctypes.c_char_p, "tpf_last_error_string": ctypes.c_char_p}
 
 ERROR_NAMES = {1: "invalid argument", 2: "unsupported", 3: "CUDA error", 4: "workspace", 5: "device status"}
 

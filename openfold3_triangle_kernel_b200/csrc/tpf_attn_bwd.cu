@@ -1,0 +1,1078 @@
+// Triangle-attention backward for sm_100a: dQ, dK, dV (this file, kernel 1), the row
+// scalar delta (kernel 0) and dBias (kernel 2 + fold).
+//
+// Reference interface replaced: turbopairformer_triangle_delta_out and
+// turbopairformer_triangle_sr_backward_out
+// (openfold3/core/kernels/turbopairformer/turbopairformer_triangle_delta.cu:343-414,
+//  openfold3/core/kernels/turbopairformer/turbopairformer_triangle_dq_dbias.cu:2526-2648).
+// Same math: P = exp(S - lse) (0 where lse = -inf), dP = dO V^T, dS = P (dP - delta),
+// dV = P^T dO, dK = scale dS^T Q, dQ = scale dS K, dBias = sum over outer rows of dS; P and dS
+// are rounded to bf16 only as UMMA operands, all accumulation is fp32, no atomics anywhere.
+//
+// Machine mapping (differs from the reference, which keeps 64-key leaves and writes bf16
+// dQ partials and dBias leaf planes to HBM):
+//  * kernel 1 owns whole (b, o, h) planes.  For each 128x128 (query, key) tile the five GEMMs
+//    run on tcgen05; dK/dV of up to KS key tiles and dQ of the current query tile stay in
+//    TMEM until complete, so for N <= 128*KS nothing but the final gradients is written.
+//    Longer sequences walk key strips and keep a per-CTA fp32 dQ running sum in a small
+//    private scratch (same thread, fixed order).
+//  * kernel 2 owns a (h, query tile, key tile) of dBias and walks the outer rows, recomputing
+//    S and dP (two cheap K = D GEMMs) and summing dS in fp32 registers in ascending o.
+//    A few independent o-chunks per tile fill the machine; their partial planes are folded
+//    in fixed order by a tiny kernel.
+#include "tpf_host.cuh"
+#include "tpf_ptx.cuh"
+
+namespace tpf {
+
+static __device__ int g_attn_bwd_status;
+
+int attn_bwd_status_fetch_and_clear(int* out) {
+  int v = 0, zero = 0;
+  TPF_CUDA_OK(cudaMemcpyFromSymbol(&v, g_attn_bwd_status, sizeof(int)));
+  if (v) TPF_CUDA_OK(cudaMemcpyToSymbol(g_attn_bwd_status, &zero, sizeof(int)));
+  *out = v;
+  return TPF_OK;
+}
+
+// =============================================================================================
+// kernel 0: delta[b,o,h,q] = sum_d dO[b,o,q,h,d] * O[b,o,q,h,d]      (HBM bound)
+// =============================================================================================
+template <int D>
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ d_out,
+                                                         const __nv_bfloat16* __restrict__ out,
+                                                         float* __restrict__ delta, int64_t rows, int H, int N) {
+  // one thread handles D/8 ... : LANES threads per (b,o,q,h) row of D elements, 8 elements each
+  constexpr int LANES = D / 8;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t r = gid / LANES;  // flat (b,o,q,h)
+  const int part = (int)(gid % LANES);
+  float acc = 0.f;
+  if (r < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(d_out + r * D + part * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(out + r * D + part * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), acc);
+      acc = fmaf(__uint_as_float(aw[i] & 0xFFFF0000u), __uint_as_float(bw[i] & 0xFFFF0000u), acc);
+    }
+  }
+#pragma unroll
+  for (int off = LANES / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (r < rows && part == 0) {
+    const int h = (int)(r % H);
+    const int64_t t = r / H;
+    const int q = (int)(t % N);
+    const int64_t bo = t / N;
+    delta[(bo * H + h) * N + q] = acc;
+  }
+}
+
+// =============================================================================================
+// kernel 1: dQ, dK, dV
+// =============================================================================================
+struct AttnBwdParams {
+  __nv_bfloat16 *dq, *dk, *dv;  // [B,O,H,N,D] contiguous
+  const float* lse;             // [B,O,H,N]
+  const float* delta;           // [B,O,H,N]
+  float* dq_scratch;            // per-CTA [N][D] fp32 when the key axis needs several strips
+  int B, O, H, N;
+  int q_tiles, k_tiles, n_strips;
+  int bias_broadcast;
+  float scale;
+  int n_items;
+};
+
+template <int D_>
+struct AttnBwdCfg {
+  static constexpr int D = D_;
+  static constexpr int KS = D <= 32 ? 3 : 1;   // key tiles whose dK/dV stay in TMEM together
+  static constexpr int NKV = 2, NQ = 2;
+  static constexpr int NB = D <= 32 ? 2 : 1;   // bias stages
+  static constexpr int SWZ = 2 * D;
+  static constexpr int TILE = 128 * D * 2;
+  static constexpr int BIAS_STAGE = 32768, PD_BYTES = 32768;
+  static constexpr int OFF_BIAS = 0;
+  static constexpr int OFF_P = OFF_BIAS + NB * BIAS_STAGE;
+  static constexpr int OFF_DS = OFF_P + PD_BYTES;
+  static constexpr int OFF_Q = OFF_DS + PD_BYTES;        // [NQ]
+  static constexpr int OFF_DO = OFF_Q + NQ * TILE;       // [NQ]
+  static constexpr int OFF_K = OFF_DO + NQ * TILE;       // [NKV]
+  static constexpr int OFF_V = OFF_K + NKV * TILE;       // [NKV]
+  static constexpr int OFF_MASK = OFF_V + NKV * TILE;    // [NKV] x 512
+  static constexpr int OFF_BAR = OFF_MASK + NKV * 512;
+  static constexpr int N_BAR = 2 * NB + 2 * NQ + 2 * NKV + 10;
+  static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
+  static constexpr int TM_S = 0, TM_DP = 128, TM_DQ = 256, TM_DK = 320, TM_DV = 320 + KS * D;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(TM_DV + KS * D <= 512, "TMEM budget");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+// Walks the (item, strip, query tile, key tile) sequence of one CTA.
+struct BwdWalk {
+  int n_items, q_tiles, k_tiles, KS, n_strips, step;
+  int item, strip, qt, kk;
+  __device__ void init(int first, int step_, int n_items_, int q_tiles_, int k_tiles_, int KS_, int n_strips_) {
+    n_items = n_items_; q_tiles = q_tiles_; k_tiles = k_tiles_; KS = KS_; n_strips = n_strips_; step = step_;
+    item = first; strip = 0; qt = 0; kk = 0;
+  }
+  __device__ bool valid() const { return item < n_items; }
+  __device__ int strip_len() const { return min(KS, k_tiles - strip * KS); }
+  __device__ int kt() const { return strip * KS + kk; }
+  __device__ bool first_kk() const { return kk == 0; }
+  __device__ bool last_kk() const { return kk == strip_len() - 1; }
+  __device__ bool first_qt() const { return qt == 0; }
+  __device__ bool last_qt() const { return qt == q_tiles - 1; }
+  __device__ void next() {
+    if (++kk < strip_len()) return;
+    kk = 0;
+    if (++qt < q_tiles) return;
+    qt = 0;
+    if (++strip < n_strips) return;
+    strip = 0;
+    item += step;
+  }
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
+                const AttnBwdParams p, int* __restrict__ status) {
+  constexpr int D = Cfg::D, KS = Cfg::KS, NKV = Cfg::NKV, NQ = Cfg::NQ, NB = Cfg::NB;
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* b_full = bars;
+  uint64_t* b_empty = b_full + NB;
+  uint64_t* q_full = b_empty + NB;
+  uint64_t* q_empty = q_full + NQ;
+  uint64_t* kv_full = q_empty + NQ;
+  uint64_t* kv_empty = kv_full + NKV;
+  uint64_t* misc = kv_empty + NKV;
+  uint64_t* s_full = misc + 0;
+  uint64_t* s_free = misc + 1;
+  uint64_t* dp_full = misc + 2;
+  uint64_t* dp_free = misc + 3;
+  uint64_t* p_ready = misc + 4;
+  uint64_t* p_free = misc + 5;
+  uint64_t* ds_ready = misc + 6;
+  uint64_t* ds_free = misc + 7;
+  uint64_t* dkv_full = misc + 8;
+  uint64_t* dkv_free = misc + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::N_BAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wctx{abort_flag, status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NB; ++s) {
+      mbar_init(&b_full[s], 1);
+      mbar_init(&b_empty[s], 8);
+    }
+    for (int s = 0; s < NQ; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    for (int s = 0; s < NKV; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 8);
+    mbar_init(dp_full, 1);
+    mbar_init(dp_free, 8);
+    mbar_init(p_ready, 8);
+    mbar_init(p_free, 1);
+    mbar_init(ds_ready, 8);
+    mbar_init(ds_free, 1);
+    mbar_init(dkv_full, 1);
+    mbar_init(dkv_free, 8);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmBias);
+    tma_prefetch_desc(&tmMask);
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto decode = [&](int item, int& b, int& o, int& h) {
+    h = item % p.H;
+    const int r = item / p.H;
+    o = r % p.O;
+    b = r / p.O;
+  };
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int q_s = 0, kv_s = 0, b_s = 0;
+      uint32_t q_ph = 1, kv_ph = 1, b_ph = 1;
+      BwdWalk w;
+      w.init(blockIdx.x, gridDim.x, p.n_items, p.q_tiles, p.k_tiles, KS, p.n_strips);
+      for (; w.valid(); w.next()) {
+        int b, o, h;
+        decode(w.item, b, o, h);
+        if (w.first_kk()) {
+          mbar_wait(&q_empty[q_s], q_ph, wctx);
+          mbar_expect_tx(&q_full[q_s], 2 * Cfg::TILE);
+          tma_load_5d(smem + Cfg::OFF_Q + q_s * Cfg::TILE, &tmQ, &q_full[q_s], 0, w.qt * 128, h, o, b);
+          tma_load_5d(smem + Cfg::OFF_DO + q_s * Cfg::TILE, &tmDO, &q_full[q_s], 0, w.qt * 128, h, o, b);
+          if (++q_s == NQ) {
+            q_s = 0;
+            q_ph ^= 1;
+          }
+        }
+        const int kt = w.kt();
+        mbar_wait(&kv_empty[kv_s], kv_ph, wctx);
+        mbar_expect_tx(&kv_full[kv_s], 2 * Cfg::TILE + 512);
+        tma_load_5d(smem + Cfg::OFF_K + kv_s * Cfg::TILE, &tmK, &kv_full[kv_s], 0, kt * 128, h, o, b);
+        tma_load_5d(smem + Cfg::OFF_V + kv_s * Cfg::TILE, &tmV, &kv_full[kv_s], 0, kt * 128, h, o, b);
+        tma_load_3d(smem + Cfg::OFF_MASK + kv_s * 512, &tmMask, &kv_full[kv_s], kt * 128, o, b);
+        if (++kv_s == NKV) {
+          kv_s = 0;
+          kv_ph ^= 1;
+        }
+        const int bb = p.bias_broadcast ? 0 : b;
+        mbar_wait(&b_empty[b_s], b_ph, wctx);
+        mbar_expect_tx(&b_full[b_s], Cfg::BIAS_STAGE);
+        tma_load_4d(smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE, &tmBias, &b_full[b_s], kt * 128, w.qt * 128, h, bb);
+        tma_load_4d(smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE + 16384, &tmBias, &b_full[b_s], kt * 128 + 64,
+                    w.qt * 128, h, bb);
+        if (++b_s == NB) {
+          b_s = 0;
+          b_ph ^= 1;
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_sd = make_idesc_bf16(128, 128, false, false);  // S, dP
+      constexpr uint32_t idesc_kv = make_idesc_bf16(128, D, true, true);      // dV, dK
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, false, true);     // dQ
+      constexpr uint32_t swz = swizzle_mode_for_bytes(Cfg::SWZ);
+      constexpr uint32_t swz128 = swizzle_mode_for_bytes(128);
+
+      // stage trackers for the "ahead" stream (S, dP) and the "behind" stream (dV, dK, dQ)
+      int aq_s = 0, akv_s = 0;
+      uint32_t aq_ph = 0, akv_ph = 0;
+      int bq_s = 0, bkv_s = 0;
+      uint32_t sfree_ph = 1, dpfree_ph = 1, pready_ph = 0, dsready_ph = 0, dkvfree_ph = 1;
+
+      BwdWalk wa, wb;  // ahead / behind
+      wa.init(blockIdx.x, gridDim.x, p.n_items, p.q_tiles, p.k_tiles, KS, p.n_strips);
+      wb = wa;
+
+      auto issue_s = [&]() {  // S of tile wa
+        if (wa.first_kk()) {
+          mbar_wait(&q_full[aq_s], aq_ph, wctx);
+        }
+        mbar_wait(&kv_full[akv_s], akv_ph, wctx);
+        mbar_wait(s_free, sfree_ph, wctx);
+        sfree_ph ^= 1;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(smem + Cfg::OFF_Q + aq_s * Cfg::TILE);
+        const uint32_t ka = smem_u32(smem + Cfg::OFF_K + akv_s * Cfg::TILE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_ss(tmem_base + Cfg::TM_S, make_smem_desc(qa + ks * 32, 16, 8 * Cfg::SWZ, swz),
+                  make_smem_desc(ka + ks * 32, 16, 8 * Cfg::SWZ, swz), idesc_sd, ks != 0);
+        umma_commit(s_full);
+      };
+      auto issue_dp = [&]() {  // dP of tile wa, then advance wa
+        mbar_wait(dp_free, dpfree_ph, wctx);
+        dpfree_ph ^= 1;
+        tc_fence_after();
+        const uint32_t da = smem_u32(smem + Cfg::OFF_DO + aq_s * Cfg::TILE);
+        const uint32_t va = smem_u32(smem + Cfg::OFF_V + akv_s * Cfg::TILE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_ss(tmem_base + Cfg::TM_DP, make_smem_desc(da + ks * 32, 16, 8 * Cfg::SWZ, swz),
+                  make_smem_desc(va + ks * 32, 16, 8 * Cfg::SWZ, swz), idesc_sd, ks != 0);
+        umma_commit(dp_full);
+        // advance the ahead stream
+        if (++akv_s == NKV) {
+          akv_s = 0;
+          akv_ph ^= 1;
+        }
+        const bool last_kk = wa.last_kk();
+        wa.next();
+        if (last_kk) {
+          if (++aq_s == NQ) {
+            aq_s = 0;
+            aq_ph ^= 1;
+          }
+        }
+      };
+
+      if (wa.valid()) {
+        issue_s();
+        issue_dp();
+      }
+      for (; wb.valid();) {
+        if (wa.valid()) issue_s();  // S of the next tile as soon as the current S sits in registers
+        // ---- dV(kt) (+)= P^T dO
+        mbar_wait(p_ready, pready_ph, wctx);
+        pready_ph ^= 1;
+        if (wb.first_qt() && wb.first_kk()) {
+          // first accumulation of a strip overwrites dK/dV: the previous strip must have been read out
+          mbar_wait(dkv_free, dkvfree_ph, wctx);
+          dkvfree_ph ^= 1;
+        }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(smem + Cfg::OFF_P);
+        const uint32_t dsa = smem_u32(smem + Cfg::OFF_DS);
+        const uint32_t qa = smem_u32(smem + Cfg::OFF_Q + bq_s * Cfg::TILE);
+        const uint32_t doa = smem_u32(smem + Cfg::OFF_DO + bq_s * Cfg::TILE);
+        const uint32_t ka = smem_u32(smem + Cfg::OFF_K + bkv_s * Cfg::TILE);
+        const uint32_t acc_kv = wb.first_qt() ? 0u : 1u;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)  // 16 queries per step
+          umma_ss(tmem_base + Cfg::TM_DV + wb.kk * D, make_smem_desc(pa + ks * 2048, 16384, 1024, swz128),
+                  make_smem_desc(doa + ks * 16 * Cfg::SWZ, 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz), idesc_kv,
+                  (ks != 0) ? 1u : acc_kv);
+        umma_commit(p_free);
+        if (wa.valid()) issue_dp();  // dP of the next tile
+        // ---- dK(kt) (+)= dS^T Q ; dQ(qt) (+)= dS K
+        mbar_wait(ds_ready, dsready_ph, wctx);
+        dsready_ph ^= 1;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ss(tmem_base + Cfg::TM_DK + wb.kk * D, make_smem_desc(dsa + ks * 2048, 16384, 1024, swz128),
+                  make_smem_desc(qa + ks * 16 * Cfg::SWZ, 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz), idesc_kv,
+                  (ks != 0) ? 1u : acc_kv);
+        const uint32_t acc_q = wb.first_kk() ? 0u : 1u;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)  // 16 keys per step
+          umma_ss(tmem_base + Cfg::TM_DQ, make_smem_desc(dsa + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, swz128),
+                  make_smem_desc(ka + ks * 16 * Cfg::SWZ, 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz), idesc_dq,
+                  (ks != 0) ? 1u : acc_q);
+        umma_commit(ds_free);
+        umma_commit(&kv_empty[bkv_s]);
+        if (++bkv_s == NKV) bkv_s = 0;
+        const bool last_kk = wb.last_kk();
+        const bool strip_done = last_kk && wb.last_qt();
+        if (last_kk) {
+          umma_commit(&q_empty[bq_s]);
+          if (++bq_s == NQ) bq_s = 0;
+        }
+        if (strip_done) umma_commit(dkv_full);
+        wb.next();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps (2 threads per query row)
+    const int hf = warp >> 2;                   // which 64-key half of the tile
+    const int row = 32 * (warp & 3) + lane;     // query row in the tile == TMEM lane
+    const uint32_t lane_base = 32 * (warp & 3);
+    const uint32_t t_s = tmem_addr(tmem_base, lane_base, Cfg::TM_S + 64 * hf);
+    const uint32_t t_dp = tmem_addr(tmem_base, lane_base, Cfg::TM_DP + 64 * hf);
+    constexpr int DH = D / 2;                   // output columns per thread
+    const uint32_t t_dq = tmem_addr(tmem_base, lane_base, Cfg::TM_DQ + DH * hf);
+    uint8_t* p_row = smem + Cfg::OFF_P + hf * 16384 + row * 128;
+    uint8_t* ds_row = smem + Cfg::OFF_DS + hf * 16384 + row * 128;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float scale = p.scale;
+
+    uint32_t sfull_ph = 0, dpfull_ph = 0, pfree_ph = 1, dsfree_ph = 1, kv_ph = 0, b_ph = 0, dkvfull_ph = 0;
+    int kv_s = 0, b_s = 0;
+    float neg_lse2 = -INFINITY, delta = 0.f;
+    bool have_prev_dq = false;  // a finished dQ tile waits in TMEM
+    int prev_q0 = 0, prev_b = 0, prev_o = 0, prev_h = 0, prev_strip = 0;
+
+    // read a finished dQ tile out of TMEM and store it (or fold it into the per-CTA running sum)
+    auto flush_dq = [&](int b, int o, int h, int q0, int strip) {
+      const int q = q0 + row;
+      float v[DH];
+#pragma unroll
+      for (int c = 0; c < DH; c += 8) {
+        uint32_t r8[8];
+        tmem_ld8(t_dq + c, r8);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c + i] = __uint_as_float(r8[i]);
+      }
+      if (q >= p.N) return;
+      if (p.n_strips > 1) {
+        float* sc = p.dq_scratch + ((int64_t)blockIdx.x * p.N + q) * D + DH * hf;
+        if (strip > 0) {
+#pragma unroll
+          for (int c = 0; c < DH; c += 4) {
+            const float4 o4 = *reinterpret_cast<const float4*>(sc + c);
+            v[c] += o4.x; v[c + 1] += o4.y; v[c + 2] += o4.z; v[c + 3] += o4.w;
+          }
+        }
+        if (strip + 1 < p.n_strips) {
+#pragma unroll
+          for (int c = 0; c < DH; c += 4) *reinterpret_cast<float4*>(sc + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+          return;
+        }
+      }
+      __nv_bfloat16* dst = p.dq + ((((int64_t)b * p.O + o) * p.H + h) * p.N + q) * D + DH * hf;
+#pragma unroll
+      for (int c = 0; c < DH; c += 8) {
+        uint4 pk;
+        pk.x = pack_bf16x2(v[c + 0] * scale, v[c + 1] * scale);
+        pk.y = pack_bf16x2(v[c + 2] * scale, v[c + 3] * scale);
+        pk.z = pack_bf16x2(v[c + 4] * scale, v[c + 5] * scale);
+        pk.w = pack_bf16x2(v[c + 6] * scale, v[c + 7] * scale);
+        *reinterpret_cast<uint4*>(dst + c) = pk;
+      }
+    };
+
+    BwdWalk w;
+    w.init(blockIdx.x, gridDim.x, p.n_items, p.q_tiles, p.k_tiles, KS, p.n_strips);
+    for (; w.valid(); w.next()) {
+      int b, o, h;
+      decode(w.item, b, o, h);
+      const int q = w.qt * 128 + row;
+      const int kt = w.kt();
+      if (w.first_kk()) {
+        if (q < p.N) {
+          const int64_t idx = (((int64_t)b * p.O + o) * p.H + h) * p.N + q;
+          const float l = p.lse[idx];
+          neg_lse2 = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
+          delta = p.delta[idx];
+        } else {
+          neg_lse2 = -INFINITY;
+          delta = 0.f;
+        }
+      }
+
+      // ---------------- phase 1: P = exp(S - lse)
+      mbar_wait(s_full, sfull_ph, wctx);
+      sfull_ph ^= 1;
+      mbar_wait(&kv_full[kv_s], kv_ph, wctx);
+      mbar_wait(&b_full[b_s], b_ph, wctx);
+      tc_fence_after();
+      const uint8_t* bias_row = smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE + hf * 16384 + row * 128;
+      const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_MASK + kv_s * 512) + 64 * hf;
+      const bool tail = (kt + 1) * 128 > p.N;
+      float pf[64];
+      uint32_t ppk[32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[16];
+        tmem_ld16(t_s + 16 * c, raw);
+        uint4 bv[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) bv[u] = *reinterpret_cast<const uint4*>(bias_row + (((2 * c + u) ^ (row & 7)) << 4));
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t bw[4] = {bv[u].x, bv[u].y, bv[u].z, bv[u].w};
+          const float4 mk0 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u);
+          const float4 mk1 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u + 4);
+          const float mk[8] = {mk0.x, mk0.y, mk0.z, mk0.w, mk1.x, mk1.y, mk1.z, mk1.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i0 = 8 * u + 2 * e;
+            float v0 = fmaf(__uint_as_float(raw[i0]), scale, __uint_as_float(bw[e] << 16)) + mk[2 * e];
+            float v1 = fmaf(__uint_as_float(raw[i0 + 1]), scale, __uint_as_float(bw[e] & 0xFFFF0000u)) + mk[2 * e + 1];
+            if (tail) {
+              if (kt * 128 + 64 * hf + 16 * c + i0 >= p.N) v0 = -INFINITY;
+              if (kt * 128 + 64 * hf + 16 * c + i0 + 1 >= p.N) v1 = -INFINITY;
+            }
+            const float p0 = ex2_approx(fmaf(v0, kLog2e, neg_lse2));
+            const float p1 = ex2_approx(fmaf(v1, kLog2e, neg_lse2));
+            pf[16 * c + i0] = p0;
+            pf[16 * c + i0 + 1] = p1;
+            ppk[8 * c + 4 * u + e] = pack_bf16x2(p0, p1);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_free);
+        mbar_arrive(&b_empty[b_s]);
+      }
+      if (++b_s == NB) {
+        b_s = 0;
+        b_ph ^= 1;
+      }
+      if (++kv_s == NKV) {
+        kv_s = 0;
+        kv_ph ^= 1;
+      }
+      // P tile -> smem (the dV UMMA of the previous tile has long finished)
+      mbar_wait(p_free, pfree_ph, wctx);
+      pfree_ph ^= 1;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        *reinterpret_cast<uint4*>(p_row + ((u ^ (row & 7)) << 4)) =
+            make_uint4(ppk[4 * u], ppk[4 * u + 1], ppk[4 * u + 2], ppk[4 * u + 3]);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+
+      // ---------------- phase 2: dS = P (dP - delta)
+      mbar_wait(dp_full, dpfull_ph, wctx);
+      dpfull_ph ^= 1;
+      tc_fence_after();
+      uint32_t dpk[32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[16];
+        tmem_ld16(t_dp + 16 * c, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          const float d0 = pf[16 * c + i] * (__uint_as_float(raw[i]) - delta);
+          const float d1 = pf[16 * c + i + 1] * (__uint_as_float(raw[i + 1]) - delta);
+          dpk[8 * c + (i >> 1)] = pack_bf16x2(d0, d1);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dp_free);
+
+      // the dK/dQ UMMAs of the previous tile are done: dS smem is free and a finished dQ can be read
+      mbar_wait(ds_free, dsfree_ph, wctx);
+      dsfree_ph ^= 1;
+      tc_fence_after();
+      if (have_prev_dq) {
+        flush_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip);
+        have_prev_dq = false;
+        tc_fence_before();
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        *reinterpret_cast<uint4*>(ds_row + ((u ^ (row & 7)) << 4)) =
+            make_uint4(dpk[4 * u], dpk[4 * u + 1], dpk[4 * u + 2], dpk[4 * u + 3]);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+
+      if (w.last_kk()) {
+        have_prev_dq = true;
+        prev_b = b; prev_o = o; prev_h = h; prev_q0 = w.qt * 128; prev_strip = w.strip;
+      }
+
+      if (w.last_kk() && w.last_qt()) {
+        // ---------------- strip epilogue: dQ of the last query tile, dK / dV of the strip
+        mbar_wait(dkv_full, dkvfull_ph, wctx);
+        dkvfull_ph ^= 1;
+        tc_fence_after();
+        flush_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip);
+        have_prev_dq = false;
+        const int nk = w.strip_len();
+        for (int kk = 0; kk < nk; ++kk) {
+          const int key = (w.strip * KS + kk) * 128 + row;
+          const int64_t base = ((((int64_t)b * p.O + o) * p.H + h) * p.N + key) * D + DH * hf;
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const uint32_t t_src = tmem_addr(tmem_base, lane_base, (which ? Cfg::TM_DV : Cfg::TM_DK) + kk * D + DH * hf);
+            const float mul = which ? 1.f : scale;
+            __nv_bfloat16* dst = (which ? p.dv : p.dk) + base;
+#pragma unroll
+            for (int c = 0; c < DH; c += 8) {
+              uint32_t r8[8];
+              tmem_ld8(t_src + c, r8);
+              tmem_ld_wait();
+              if (key < p.N) {
+                uint4 pk;
+                pk.x = pack_bf16x2(__uint_as_float(r8[0]) * mul, __uint_as_float(r8[1]) * mul);
+                pk.y = pack_bf16x2(__uint_as_float(r8[2]) * mul, __uint_as_float(r8[3]) * mul);
+                pk.z = pack_bf16x2(__uint_as_float(r8[4]) * mul, __uint_as_float(r8[5]) * mul);
+                pk.w = pack_bf16x2(__uint_as_float(r8[6]) * mul, __uint_as_float(r8[7]) * mul);
+                *reinterpret_cast<uint4*>(dst + c) = pk;
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dkv_free);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// =============================================================================================
+// kernel 2: dBias partial planes.  One CTA = one (group, h, query tile, key tile) and a chunk of
+// outer planes; dS summed over the chunk in ascending plane order, fp32, in registers.
+// =============================================================================================
+struct AttnDbiasParams {
+  float* part;        // [n_chunks][G][H][N][N] fp32 (or the final buffer when n_chunks == 1)
+  const float* lse;   // [B,O,H,N]
+  const float* delta; // [B,O,H,N]
+  int B, O, H, N;
+  int G;              // bias batch (1 or B)
+  int planes;         // outer planes per group = (B / G) * O
+  int n_chunks, chunk_len;
+  int q_tiles, k_tiles;
+  float scale;
+};
+
+template <int D_>
+struct AttnDbiasCfg {
+  static constexpr int D = D_;
+  static constexpr int SWZ = 2 * D;
+  static constexpr int TILE = 128 * D * 2;
+  static constexpr int STAGE = 4 * TILE + 1024;  // Q, dO, K, V, mask row
+  static constexpr int NST = D <= 32 ? 4 : 2;
+  static constexpr int OFF_BIAS = 0;
+  static constexpr int OFF_ST = 32768;
+  static constexpr int OFF_BAR = OFF_ST + NST * STAGE;
+  static constexpr int N_BAR = 2 * NST + 4 + 1;
+  static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(320, 1)
+attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                  const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
+                  const AttnDbiasParams p, int* __restrict__ status) {
+  constexpr int D = Cfg::D, NST = Cfg::NST;
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* full = bars;
+  uint64_t* empty = full + NST;
+  uint64_t* sdp_full = empty + NST;   // [2]
+  uint64_t* sdp_free = sdp_full + 2;  // [2]
+  uint64_t* bias_full = sdp_free + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::N_BAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wctx{abort_flag, status};
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // work item
+  int it = blockIdx.x;
+  const int chunk = it % p.n_chunks; it /= p.n_chunks;
+  const int kt = it % p.k_tiles; it /= p.k_tiles;
+  const int qt = it % p.q_tiles; it /= p.q_tiles;
+  const int h = it % p.H;
+  const int g = it / p.H;
+  const int pl0 = chunk * p.chunk_len;
+  const int pl1 = min(p.planes, pl0 + p.chunk_len);
+  const int b_per_g = p.B / p.G;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 9);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sdp_full[s], 1);
+      mbar_init(&sdp_free[s], 8);
+    }
+    mbar_init(bias_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmBias);
+    tma_prefetch_desc(&tmMask);
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      mbar_expect_tx(bias_full, 32768);
+      tma_load_4d(smem + Cfg::OFF_BIAS, &tmBias, bias_full, kt * 128, qt * 128, h, g);
+      tma_load_4d(smem + Cfg::OFF_BIAS + 16384, &tmBias, bias_full, kt * 128 + 64, qt * 128, h, g);
+      int s = 0;
+      uint32_t ph = 1;
+      for (int pl = pl0; pl < pl1; ++pl) {
+        const int b = g * b_per_g + pl / p.O, o = pl % p.O;
+        mbar_wait(&empty[s], ph, wctx);
+        mbar_expect_tx(&full[s], 4 * Cfg::TILE + 512);
+        uint8_t* st = smem + Cfg::OFF_ST + s * Cfg::STAGE;
+        tma_load_5d(st, &tmQ, &full[s], 0, qt * 128, h, o, b);
+        tma_load_5d(st + Cfg::TILE, &tmDO, &full[s], 0, qt * 128, h, o, b);
+        tma_load_5d(st + 2 * Cfg::TILE, &tmK, &full[s], 0, kt * 128, h, o, b);
+        tma_load_5d(st + 3 * Cfg::TILE, &tmV, &full[s], 0, kt * 128, h, o, b);
+        tma_load_3d(st + 4 * Cfg::TILE, &tmMask, &full[s], kt * 128, o, b);
+        if (++s == NST) {
+          s = 0;
+          ph ^= 1;
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t swz = swizzle_mode_for_bytes(Cfg::SWZ);
+      int s = 0, buf = 0;
+      uint32_t ph = 0, free_ph[2] = {1, 1};
+      for (int pl = pl0; pl < pl1; ++pl) {
+        mbar_wait(&full[s], ph, wctx);
+        mbar_wait(&sdp_free[buf], free_ph[buf], wctx);
+        free_ph[buf] ^= 1;
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + Cfg::OFF_ST + s * Cfg::STAGE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_ss(tmem_base + buf * 256, make_smem_desc(st + ks * 32, 16, 8 * Cfg::SWZ, swz),
+                  make_smem_desc(st + 2 * Cfg::TILE + ks * 32, 16, 8 * Cfg::SWZ, swz), idesc, ks != 0);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_ss(tmem_base + buf * 256 + 128, make_smem_desc(st + Cfg::TILE + ks * 32, 16, 8 * Cfg::SWZ, swz),
+                  make_smem_desc(st + 3 * Cfg::TILE + ks * 32, 16, 8 * Cfg::SWZ, swz), idesc, ks != 0);
+        umma_commit(&sdp_full[buf]);
+        umma_commit(&empty[s]);
+        buf ^= 1;
+        if (++s == NST) {
+          s = 0;
+          ph ^= 1;
+        }
+      }
+    }
+  } else {
+    const int hf = warp >> 2;
+    const int row = 32 * (warp & 3) + lane;
+    const uint32_t lane_base = 32 * (warp & 3);
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float scale = p.scale;
+    const int q = qt * 128 + row;
+    const bool tail = (kt + 1) * 128 > p.N;
+
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+
+    // bias row (64 bf16) -> packed registers
+    mbar_wait(bias_full, 0, wctx);
+    uint32_t bpk[32];
+    {
+      const uint8_t* brow = smem + Cfg::OFF_BIAS + hf * 16384 + row * 128;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint4 v4 = *reinterpret_cast<const uint4*>(brow + ((u ^ (row & 7)) << 4));
+        bpk[4 * u] = v4.x; bpk[4 * u + 1] = v4.y; bpk[4 * u + 2] = v4.z; bpk[4 * u + 3] = v4.w;
+      }
+    }
+
+    auto load_row_scalars = [&](int pl, float& nl2, float& dl) {
+      nl2 = -INFINITY;
+      dl = 0.f;
+      if (pl < pl1 && q < p.N) {
+        const int b = g * b_per_g + pl / p.O, o = pl % p.O;
+        const int64_t idx = (((int64_t)b * p.O + o) * p.H + h) * p.N + q;
+        const float l = p.lse[idx];
+        nl2 = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
+        dl = p.delta[idx];
+      }
+    };
+
+    int s = 0, buf = 0;
+    uint32_t ph = 0, full_ph[2] = {0, 0};
+    float nl2_next, dl_next;
+    load_row_scalars(pl0, nl2_next, dl_next);
+    for (int pl = pl0; pl < pl1; ++pl) {
+      const float neg_lse2 = nl2_next, delta = dl_next;
+      load_row_scalars(pl + 1, nl2_next, dl_next);
+      mbar_wait(&sdp_full[buf], full_ph[buf], wctx);
+      full_ph[buf] ^= 1;
+      mbar_wait(&full[s], ph, wctx);
+      tc_fence_after();
+      const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_ST + s * Cfg::STAGE + 4 * Cfg::TILE) + 64 * hf;
+      const uint32_t t_s = tmem_addr(tmem_base, lane_base, buf * 256 + 64 * hf);
+      const uint32_t t_dp = tmem_addr(tmem_base, lane_base, buf * 256 + 128 + 64 * hf);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[16], rd[16];
+        tmem_ld16(t_s + 16 * c, rs);
+        tmem_ld16(t_dp + 16 * c, rd);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const float4 mk0 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u);
+          const float4 mk1 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u + 4);
+          const float mk[8] = {mk0.x, mk0.y, mk0.z, mk0.w, mk1.x, mk1.y, mk1.z, mk1.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i0 = 8 * u + 2 * e;
+            const uint32_t bw = bpk[8 * c + 4 * u + e];
+            float v0 = fmaf(__uint_as_float(rs[i0]), scale, __uint_as_float(bw << 16)) + mk[2 * e];
+            float v1 = fmaf(__uint_as_float(rs[i0 + 1]), scale, __uint_as_float(bw & 0xFFFF0000u)) + mk[2 * e + 1];
+            if (tail) {
+              if (kt * 128 + 64 * hf + 16 * c + i0 >= p.N) v0 = -INFINITY;
+              if (kt * 128 + 64 * hf + 16 * c + i0 + 1 >= p.N) v1 = -INFINITY;
+            }
+            const float p0 = ex2_approx(fmaf(v0, kLog2e, neg_lse2));
+            const float p1 = ex2_approx(fmaf(v1, kLog2e, neg_lse2));
+            acc[16 * c + i0] = fmaf(p0, __uint_as_float(rd[i0]) - delta, acc[16 * c + i0]);
+            acc[16 * c + i0 + 1] = fmaf(p1, __uint_as_float(rd[i0 + 1]) - delta, acc[16 * c + i0 + 1]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&sdp_free[buf]);
+        mbar_arrive(&empty[s]);
+      }
+      buf ^= 1;
+      if (++s == NST) {
+        s = 0;
+        ph ^= 1;
+      }
+    }
+
+    if (q < p.N) {
+      const int k0 = kt * 128 + 64 * hf;
+      float* dst = p.part + ((((int64_t)chunk * p.G + g) * p.H + h) * p.N + q) * p.N + k0;
+      if ((p.N & 3) == 0 && k0 + 64 <= p.N) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 4)
+          *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (k0 + i < p.N) dst[i] = acc[i];
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// dbias[i] = ((part[0][i] + part[1][i]) + part[2][i]) + ...   (ascending chunk order, fp32)
+__global__ void __launch_bounds__(256) attn_dbias_fold_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                              int64_t n, int n_chunks) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float a = part[i];
+    for (int c = 1; c < n_chunks; ++c) a = __fadd_rn(a, part[(int64_t)c * n + i]);
+    out[i] = a;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+int make_qkv_tmap(CUtensorMap* tm, const void* base, int64_t B, int64_t O, int64_t H, int64_t N, int64_t D,
+                  const int64_t* st, int swz);
+int make_bias_tmap(CUtensorMap* tm, const void* base, int64_t Bb, int64_t H, int64_t N, int64_t pitch);
+int make_mask_tmap(CUtensorMap* tm, const void* base, int64_t B, int64_t O, int64_t N, int64_t pitch);
+
+template <int D>
+int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                    const CUtensorMap& tb, const CUtensorMap& tmk, AttnBwdParams& p, int* status, int grid,
+                    cudaStream_t stream) {
+  using Cfg = AttnBwdCfg<D>;
+  auto kern = attn_bwd_kernel<Cfg>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    attr_done = true;
+  }
+  kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
+  TPF_CUDA_OK(cudaGetLastError());
+  return TPF_OK;
+}
+
+static int bwd_key_strip(int64_t D) { return D <= 32 ? 3 : 1; }
+
+int64_t attn_bwd_workspace_bytes(int64_t B, int64_t O, int64_t H, int64_t N, int64_t D) {
+  const int64_t k_tiles = (N + 127) / 128;
+  const int64_t strips = (k_tiles + bwd_key_strip(D) - 1) / bwd_key_strip(D);
+  if (strips <= 1) return 0;
+  int64_t grid = sm_count();
+  if (grid > B * O * H) grid = B * O * H;
+  return grid * N * D * 4;
+}
+
+int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
+                  const int64_t* k_strides, const int64_t* v_strides, const void* out, const float* lse,
+                  const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                  void* dq, void* dk, void* dv, float* delta, void* workspace, int64_t workspace_bytes, int64_t B,
+                  int64_t O, int64_t H, int64_t N, int64_t D, float scale, cudaStream_t stream) {
+  TPF_REQUIRE(q && k && v && d_out && out && lse && mask && bias && dq && dk && dv && delta, TPF_ERR_INVALID_ARGUMENT,
+              "attn_bwd: null pointer");
+  TPF_REQUIRE(B > 0 && O > 0 && H > 0 && N > 0, TPF_ERR_INVALID_ARGUMENT, "attn_bwd: B,O,H,N must be positive");
+  TPF_REQUIRE(D == 16 || D == 32 || D == 64, TPF_ERR_UNSUPPORTED, "attn_bwd: head dim %lld not in {16,32,64}",
+              (long long)D);
+  TPF_REQUIRE(bias_batch == 1 || bias_batch == B, TPF_ERR_INVALID_ARGUMENT, "attn_bwd: bias batch must be 1 or B");
+  TPF_REQUIRE(bias_pitch >= N && bias_pitch % 8 == 0, TPF_ERR_INVALID_ARGUMENT,
+              "attn_bwd: bias row pitch must be >= N and a multiple of 8 elements");
+  TPF_REQUIRE(mask_pitch >= N && mask_pitch % 4 == 0, TPF_ERR_INVALID_ARGUMENT,
+              "attn_bwd: mask row pitch must be >= N and a multiple of 4 elements");
+  TPF_REQUIRE(B * O * H < (1ll << 31) && N <= (1 << 24), TPF_ERR_INVALID_ARGUMENT, "attn_bwd: extent too large");
+  const int64_t need = attn_bwd_workspace_bytes(B, O, H, N, D);
+  TPF_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), TPF_ERR_WORKSPACE,
+              "attn_bwd: workspace of %lld bytes required, %lld given", (long long)need, (long long)workspace_bytes);
+
+  // delta = rowsum(dO * O)
+  {
+    const int64_t rows = B * O * N * H;
+    const int lanes = (int)D / 8;
+    const int64_t threads = rows * lanes;
+    const int64_t blocks = (threads + 255) / 256;
+    TPF_REQUIRE(blocks < (1ll << 31), TPF_ERR_INVALID_ARGUMENT, "attn_bwd: too many rows");
+    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(d_out);
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(out);
+    if (D == 16) attn_delta_kernel<16><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
+    else if (D == 32) attn_delta_kernel<32><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
+    else attn_delta_kernel<64><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+
+  const int swz = 2 * (int)D;
+  CUtensorMap tq, tk, tv, tdo, tb, tm;
+  int rc;
+  if ((rc = make_qkv_tmap(&tq, q, B, O, H, N, D, q_strides, swz))) return rc;
+  if ((rc = make_qkv_tmap(&tk, k, B, O, H, N, D, k_strides, swz))) return rc;
+  if ((rc = make_qkv_tmap(&tv, v, B, O, H, N, D, v_strides, swz))) return rc;
+  const int64_t do_strides[4] = {O * N * H * D, N * H * D, D, H * D};  // d_out is [B,O,N,H,D]
+  if ((rc = make_qkv_tmap(&tdo, d_out, B, O, H, N, D, do_strides, swz))) return rc;
+  if ((rc = make_bias_tmap(&tb, bias, bias_batch, H, N, bias_pitch))) return rc;
+  if ((rc = make_mask_tmap(&tm, mask, B, O, N, mask_pitch))) return rc;
+
+  AttnBwdParams p;
+  p.dq = reinterpret_cast<__nv_bfloat16*>(dq);
+  p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.lse = lse;
+  p.delta = delta;
+  p.dq_scratch = reinterpret_cast<float*>(workspace);
+  p.B = (int)B; p.O = (int)O; p.H = (int)H; p.N = (int)N;
+  p.q_tiles = (int)((N + 127) / 128);
+  p.k_tiles = p.q_tiles;
+  const int ks = bwd_key_strip(D);
+  p.n_strips = (p.k_tiles + ks - 1) / ks;
+  p.bias_broadcast = bias_batch == 1 && B > 1 ? 1 : 0;
+  p.scale = scale;
+  p.n_items = (int)(B * O * H);
+  int grid = sm_count();
+  if (grid > p.n_items) grid = p.n_items;
+  int* status = nullptr;
+  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_attn_bwd_status));
+  if (D == 16) return launch_attn_bwd<16>(tq, tk, tv, tdo, tb, tm, p, status, grid, stream);
+  if (D == 32) return launch_attn_bwd<32>(tq, tk, tv, tdo, tb, tm, p, status, grid, stream);
+  return launch_attn_bwd<64>(tq, tk, tv, tdo, tb, tm, p, status, grid, stream);
+}
+
+template <int D>
+int launch_attn_dbias(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                      const CUtensorMap& tb, const CUtensorMap& tmk, AttnDbiasParams& p, int* status, int grid,
+                      cudaStream_t stream) {
+  using Cfg = AttnDbiasCfg<D>;
+  auto kern = attn_dbias_kernel<Cfg>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    attr_done = true;
+  }
+  kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
+  TPF_CUDA_OK(cudaGetLastError());
+  return TPF_OK;
+}
+
+// How the outer planes of one dBias tile are split into independent chunks.
+static void dbias_plan(int64_t B, int64_t O, int64_t H, int64_t N, int64_t G, int* n_chunks, int* chunk_len) {
+  const int64_t tiles = G * H * ((N + 127) / 128) * ((N + 127) / 128);
+  const int64_t planes = (B / G) * O;
+  int64_t c = sm_count() / tiles;
+  if (c < 1) c = 1;
+  if (c > planes) c = planes;
+  const int64_t len = (planes + c - 1) / c;
+  c = (planes + len - 1) / len;
+  *n_chunks = (int)c;
+  *chunk_len = (int)len;
+}
+
+int64_t attn_dbias_workspace_bytes(int64_t B, int64_t O, int64_t H, int64_t N, int64_t G) {
+  int c, len;
+  dbias_plan(B, O, H, N, G, &c, &len);
+  return c > 1 ? (int64_t)c * G * H * N * N * 4 : 0;
+}
+
+int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
+                   const int64_t* k_strides, const int64_t* v_strides, const float* lse, const float* delta,
+                   const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                   float* dbias, void* workspace, int64_t workspace_bytes, int64_t B, int64_t O, int64_t H, int64_t N,
+                   int64_t D, float scale, cudaStream_t stream) {
+  TPF_REQUIRE(dbias != nullptr, TPF_ERR_INVALID_ARGUMENT, "attn_bwd: dbias is NULL");
+  const int64_t G = bias_batch;
+  int n_chunks, chunk_len;
+  dbias_plan(B, O, H, N, G, &n_chunks, &chunk_len);
+  const int64_t need = attn_dbias_workspace_bytes(B, O, H, N, G);
+  TPF_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), TPF_ERR_WORKSPACE,
+              "attn_bwd: dBias workspace of %lld bytes required, %lld given", (long long)need,
+              (long long)workspace_bytes);
+  const int swz = 2 * (int)D;
+  CUtensorMap tq, tk, tv, tdo, tb, tm;
+  int rc;
+  if ((rc = make_qkv_tmap(&tq, q, B, O, H, N, D, q_strides, swz))) return rc;
+  if ((rc = make_qkv_tmap(&tk, k, B, O, H, N, D, k_strides, swz))) return rc;
+  if ((rc = make_qkv_tmap(&tv, v, B, O, H, N, D, v_strides, swz))) return rc;
+  const int64_t do_strides[4] = {O * N * H * D, N * H * D, D, H * D};
+  if ((rc = make_qkv_tmap(&tdo, d_out, B, O, H, N, D, do_strides, swz))) return rc;
+  if ((rc = make_bias_tmap(&tb, bias, bias_batch, H, N, bias_pitch))) return rc;
+  if ((rc = make_mask_tmap(&tm, mask, B, O, N, mask_pitch))) return rc;
+  AttnDbiasParams p;
+  p.part = n_chunks > 1 ? reinterpret_cast<float*>(workspace) : dbias;
+  p.lse = lse;
+  p.delta = delta;
+  p.B = (int)B; p.O = (int)O; p.H = (int)H; p.N = (int)N;
+  p.G = (int)G;
+  p.planes = (int)((B / G) * O);
+  p.n_chunks = n_chunks;
+  p.chunk_len = chunk_len;
+  p.q_tiles = (int)((N + 127) / 128);
+  p.k_tiles = p.q_tiles;
+  p.scale = scale;
+  const int64_t grid = (int64_t)G * H * p.q_tiles * p.k_tiles * n_chunks;
+  TPF_REQUIRE(grid < (1ll << 31), TPF_ERR_INVALID_ARGUMENT, "attn_bwd: dBias grid too large");
+  int* status = nullptr;
+  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_attn_bwd_status));
+  if (D == 16) rc = launch_attn_dbias<16>(tq, tk, tv, tdo, tb, tm, p, status, (int)grid, stream);
+  else if (D == 32) rc = launch_attn_dbias<32>(tq, tk, tv, tdo, tb, tm, p, status, (int)grid, stream);
+  else rc = launch_attn_dbias<64>(tq, tk, tv, tdo, tb, tm, p, status, (int)grid, stream);
+  if (rc) return rc;
+  if (n_chunks > 1) {
+    const int64_t n = G * H * N * N;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+    attn_dbias_fold_kernel<<<blocks, 256, 0, stream>>>(p.part, dbias, n, n_chunks);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+  return TPF_OK;
+}
+
+}  // namespace tpf

@@ -20,6 +20,20 @@ int attn_fwd(const void* q, const void* k, const void* v, const int64_t* q_strid
              int64_t bias_batch, void* out, float* lse, int64_t B, int64_t O, int64_t H, int64_t N, int64_t D,
              float scale, cudaStream_t stream);
 
+int attn_bwd_status_fetch_and_clear(int* out);
+int64_t attn_bwd_workspace_bytes(int64_t B, int64_t O, int64_t H, int64_t N, int64_t D);
+int64_t attn_dbias_workspace_bytes(int64_t B, int64_t O, int64_t H, int64_t N, int64_t G);
+int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
+                  const int64_t* k_strides, const int64_t* v_strides, const void* out, const float* lse,
+                  const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                  void* dq, void* dk, void* dv, float* delta, void* workspace, int64_t workspace_bytes, int64_t B,
+                  int64_t O, int64_t H, int64_t N, int64_t D, float scale, cudaStream_t stream);
+int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
+                   const int64_t* k_strides, const int64_t* v_strides, const float* lse, const float* delta,
+                   const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                   float* dbias, void* workspace, int64_t workspace_bytes, int64_t B, int64_t O, int64_t H, int64_t N,
+                   int64_t D, float scale, cudaStream_t stream);
+
 }  // namespace tpf
 
 extern "C" {
@@ -35,6 +49,8 @@ int tpf_device_status(int* status) {
   if (rc) return rc;
   total |= v;
   if ((rc = tpf::attn_fwd_status_fetch_and_clear(&v))) return rc;
+  total |= v;
+  if ((rc = tpf::attn_bwd_status_fetch_and_clear(&v))) return rc;
   total |= v;
   *status = total;
   return TPF_OK;
@@ -55,6 +71,38 @@ int tpf_attn_fwd(const void* q, const void* k, const void* v, const int64_t* q_s
   TPF_REQUIRE(q_strides && k_strides && v_strides, TPF_ERR_INVALID_ARGUMENT, "tpf_attn_fwd: stride arrays are NULL");
   return tpf::attn_fwd(q, k, v, q_strides, k_strides, v_strides, mask, mask_pitch, bias, bias_pitch, bias_batch, out,
                        lse, B, O, H, N, D, scale, static_cast<cudaStream_t>(stream));
+}
+
+static int64_t round_up_256(int64_t x) { return (x + 255) / 256 * 256; }
+
+int64_t tpf_attn_bwd_workspace_bytes(int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, int64_t bias_batch) {
+  if (B <= 0 || O <= 0 || H <= 0 || N <= 0 || (bias_batch != 1 && bias_batch != B)) return 0;
+  return round_up_256(tpf::attn_bwd_workspace_bytes(B, O, H, N, D)) +
+         round_up_256(tpf::attn_dbias_workspace_bytes(B, O, H, N, bias_batch));
+}
+
+int tpf_attn_bwd(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
+                 const int64_t* k_strides, const int64_t* v_strides, const void* out, const float* lse,
+                 const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                 void* dq, void* dk, void* dv, float* dbias, float* delta, void* workspace, int64_t workspace_bytes,
+                 int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, void* stream) {
+  TPF_REQUIRE(q_strides && k_strides && v_strides, TPF_ERR_INVALID_ARGUMENT, "tpf_attn_bwd: stride arrays are NULL");
+  TPF_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, TPF_ERR_INVALID_ARGUMENT,
+              "tpf_attn_bwd: workspace must be 256-byte aligned");
+  TPF_REQUIRE(B > 0 && O > 0 && H > 0 && N > 0 && (bias_batch == 1 || bias_batch == B), TPF_ERR_INVALID_ARGUMENT,
+              "tpf_attn_bwd: bad extents");
+  const int64_t ws_a = round_up_256(tpf::attn_bwd_workspace_bytes(B, O, H, N, D));
+  const int64_t ws_b = round_up_256(tpf::attn_dbias_workspace_bytes(B, O, H, N, bias_batch));
+  TPF_REQUIRE(workspace_bytes >= ws_a + ws_b && (ws_a + ws_b == 0 || workspace), TPF_ERR_WORKSPACE,
+              "tpf_attn_bwd: workspace of %lld bytes required, %lld given", (long long)(ws_a + ws_b),
+              (long long)workspace_bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = tpf::attn_bwd_dqkv(q, k, v, d_out, q_strides, k_strides, v_strides, out, lse, mask, mask_pitch, bias,
+                              bias_pitch, bias_batch, dq, dk, dv, delta, workspace, ws_a, B, O, H, N, D, scale, st);
+  if (rc) return rc;
+  return tpf::attn_bwd_dbias(q, k, v, d_out, q_strides, k_strides, v_strides, lse, delta, mask, mask_pitch, bias,
+                             bias_pitch, bias_batch, dbias, static_cast<char*>(workspace) + ws_a, ws_b, B, O, H, N, D,
+                             scale, st);
 }
 
 }  // extern "C"
