@@ -95,6 +95,49 @@ int tpf_attn_bwd(const void* q, const void* k, const void* v, const void* d_out,
                  void* workspace, int64_t workspace_bytes,
                  int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, void* stream);
 
+/* Scratch sizes of the TriMul entry points (bytes; 256-byte aligned buffers). */
+int64_t tpf_trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
+int64_t tpf_trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
+
+/* Triangle multiplicative update, forward.  direction: 0 = outgoing, 1 = incoming.
+ *   z        bf16 [B,N,N,C] contiguous, C in {32,64,96,128}, N a multiple of 8
+ *   mask     fp32 [B,N,N] (1 keeps, 0 drops)
+ *   weights  fp32 masters: p_in [2C,C] = cat[a_p,b_p], g_in [2C,C] = cat[a_g,b_g],
+ *            p_out [C,C] (linear_z), g_out [C,C] (linear_g); LayerNorm vectors fp32 [C]
+ *   out      bf16 [B,N,N,C]
+ *   saved state for the backward pass, all caller-allocated:
+ *            zln, gate, xln bf16 [B*N*N,C]; a_cm, b_cm, x_cm bf16 [B*C,N*N] (channel-major);
+ *            mean_in, rstd_in, mean_out, rstd_out fp32 [B*N*N]
+ * Replaces trimul_in_fwd + torch.bmm + trimul_out_fwd
+ * (openfold3/core/kernels/turbopairformer/turbopairformer_trimul_cuda.cu:1049-1166, 1472-1530;
+ *  openfold3/core/kernels/turbopairformer/turbopairformer_trimul.py:184-292). */
+int tpf_trimul_fwd(const void* z, const float* mask,
+                   const float* p_in, const float* g_in, const float* p_out, const float* g_out,
+                   const float* norm_in_w, const float* norm_in_b, const float* norm_out_w, const float* norm_out_b,
+                   int direction, int64_t B, int64_t N, int64_t C,
+                   void* out, void* zln, float* mean_in, float* rstd_in, void* a_cm, void* b_cm, void* gate,
+                   void* x_cm, void* xln, float* mean_out, float* rstd_out,
+                   void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Triangle multiplicative update, backward.  Inputs: d_out bf16 [B,N,N,C], the forward's inputs and
+ * saved state.  Outputs: d_z bf16 [B,N,N,C]; fp32 weight gradients d_p_in [2C,C], d_g_in [2C,C],
+ * d_p_out [C,C], d_g_out [C,C]; fp32 LayerNorm gradients [C] each.  Weight gradients are split-K
+ * sums folded in ascending order (no atomics).
+ * Replaces sig_mul_bwd_out, transpose_ln_bwd, trimul_gate_split_bwd, ln_bwd_dx, ln_bwd_dgb,
+ * trimul_wgrad_fixed_fold and the cuBLAS calls between them
+ * (openfold3/core/kernels/turbopairformer/turbopairformer_trimul_cuda.cu:1789-2171;
+ *  openfold3/core/kernels/turbopairformer/turbopairformer_trimul.py:295-392). */
+int tpf_trimul_bwd(const void* d_out, const void* z, const float* mask,
+                   const float* p_in, const float* g_in, const float* p_out, const float* g_out,
+                   const float* norm_in_w, const float* norm_out_w,
+                   int direction, int64_t B, int64_t N, int64_t C,
+                   const void* out, const void* zln, const float* mean_in, const float* rstd_in,
+                   const void* a_cm, const void* b_cm, const void* gate, const void* x_cm, const void* xln,
+                   const float* mean_out, const float* rstd_out,
+                   void* d_z, float* d_p_in, float* d_g_in, float* d_p_out, float* d_g_out,
+                   float* d_norm_in_w, float* d_norm_in_b, float* d_norm_out_w, float* d_norm_out_b,
+                   void* workspace, int64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,6 +34,22 @@ int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_ou
                    float* dbias, void* workspace, int64_t workspace_bytes, int64_t B, int64_t O, int64_t H, int64_t N,
                    int64_t D, float scale, cudaStream_t stream);
 
+int trimul_status_fetch_and_clear(int* out);
+int64_t trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
+int64_t trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
+int trimul_fwd(const void* z, const float* mask, const float* p_in, const float* g_in, const float* p_out,
+               const float* g_out, const float* gin, const float* bin, const float* gout, const float* bout,
+               int incoming, int64_t B, int64_t N, int64_t C, void* out, void* zln, float* mean_in, float* rstd_in,
+               void* a_cm, void* b_cm, void* gate, void* x_cm, void* xln, float* mean_out, float* rstd_out,
+               void* workspace, int64_t workspace_bytes, cudaStream_t stream);
+int trimul_bwd(const void* d_out, const void* z, const float* mask, const float* p_in, const float* g_in,
+               const float* p_out, const float* g_out, const float* gin, const float* gout, int incoming, int64_t B,
+               int64_t N, int64_t C, const void* out, const void* zln, const float* mean_in, const float* rstd_in,
+               const void* a_cm, const void* b_cm, const void* gate, const void* x_cm, const void* xln,
+               const float* mean_out, const float* rstd_out, void* d_z, float* d_p_in, float* d_g_in, float* d_p_out,
+               float* d_g_out, float* d_gin, float* d_bin, float* d_gout, float* d_bout, void* workspace,
+               int64_t workspace_bytes, cudaStream_t stream);
+
 }  // namespace tpf
 
 extern "C" {
@@ -51,6 +67,8 @@ int tpf_device_status(int* status) {
   if ((rc = tpf::attn_fwd_status_fetch_and_clear(&v))) return rc;
   total |= v;
   if ((rc = tpf::attn_bwd_status_fetch_and_clear(&v))) return rc;
+  total |= v;
+  if ((rc = tpf::trimul_status_fetch_and_clear(&v))) return rc;
   total |= v;
   *status = total;
   return TPF_OK;
@@ -103,6 +121,46 @@ int tpf_attn_bwd(const void* q, const void* k, const void* v, const void* d_out,
   return tpf::attn_bwd_dbias(q, k, v, d_out, q_strides, k_strides, v_strides, lse, delta, mask, mask_pitch, bias,
                              bias_pitch, bias_batch, dbias, static_cast<char*>(workspace) + ws_a, ws_b, B, O, H, N, D,
                              scale, st);
+}
+
+static bool trimul_shape_ok(int64_t B, int64_t N, int64_t C) {
+  return B > 0 && N > 0 && (C == 32 || C == 64 || C == 96 || C == 128);
+}
+
+int64_t tpf_trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C) {
+  return trimul_shape_ok(B, N, C) ? tpf::trimul_fwd_workspace_bytes(B, N, C) : 0;
+}
+
+int64_t tpf_trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C) {
+  return trimul_shape_ok(B, N, C) ? tpf::trimul_bwd_workspace_bytes(B, N, C) : 0;
+}
+
+int tpf_trimul_fwd(const void* z, const float* mask, const float* p_in, const float* g_in, const float* p_out,
+                   const float* g_out, const float* norm_in_w, const float* norm_in_b, const float* norm_out_w,
+                   const float* norm_out_b, int direction, int64_t B, int64_t N, int64_t C, void* out, void* zln,
+                   float* mean_in, float* rstd_in, void* a_cm, void* b_cm, void* gate, void* x_cm, void* xln,
+                   float* mean_out, float* rstd_out, void* workspace, int64_t workspace_bytes, void* stream) {
+  TPF_REQUIRE(direction == 0 || direction == 1, TPF_ERR_INVALID_ARGUMENT,
+              "tpf_trimul_fwd: direction must be 0 (outgoing) or 1 (incoming)");
+  return tpf::trimul_fwd(z, mask, p_in, g_in, p_out, g_out, norm_in_w, norm_in_b, norm_out_w, norm_out_b, direction, B,
+                         N, C, out, zln, mean_in, rstd_in, a_cm, b_cm, gate, x_cm, xln, mean_out, rstd_out, workspace,
+                         workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int tpf_trimul_bwd(const void* d_out, const void* z, const float* mask, const float* p_in, const float* g_in,
+                   const float* p_out, const float* g_out, const float* norm_in_w, const float* norm_out_w,
+                   int direction, int64_t B, int64_t N, int64_t C, const void* out, const void* zln,
+                   const float* mean_in, const float* rstd_in, const void* a_cm, const void* b_cm, const void* gate,
+                   const void* x_cm, const void* xln, const float* mean_out, const float* rstd_out, void* d_z,
+                   float* d_p_in, float* d_g_in, float* d_p_out, float* d_g_out, float* d_norm_in_w,
+                   float* d_norm_in_b, float* d_norm_out_w, float* d_norm_out_b, void* workspace,
+                   int64_t workspace_bytes, void* stream) {
+  TPF_REQUIRE(direction == 0 || direction == 1, TPF_ERR_INVALID_ARGUMENT,
+              "tpf_trimul_bwd: direction must be 0 (outgoing) or 1 (incoming)");
+  return tpf::trimul_bwd(d_out, z, mask, p_in, g_in, p_out, g_out, norm_in_w, norm_out_w, direction, B, N, C, out, zln,
+                         mean_in, rstd_in, a_cm, b_cm, gate, x_cm, xln, mean_out, rstd_out, d_z, d_p_in, d_g_in,
+                         d_p_out, d_g_out, d_norm_in_w, d_norm_in_b, d_norm_out_w, d_norm_out_b, workspace,
+                         workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -35,12 +35,14 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int CHUNK_A = SWZ_A / 2;  // MN-major: elements per swizzle row
   static constexpr int CHUNK_B = SWZ_B / 2;
-  static constexpr int TMEM_COLS = 2 * BN;   // two accumulators
+  static constexpr int ACC_STRIDE = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;  // TMEM columns per accumulator
+  static constexpr int TMEM_COLS = 2 * ACC_STRIDE;  // two accumulators; power of two >= 32
   static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 256 + 1024;
   static_assert(BM == 128, "UMMA tile M is 128 (one TMEM lane per row)");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
   static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
                 "TMEM allocation must be a power of two >= 32");
+  static_assert(BN % 32 == 0, "the epilogue walks 32 accumulator columns at a time");
   static_assert(A_BYTES % 1024 == 0 && B_BYTES % 1024 == 0, "stage buffers keep 1024-byte alignment");
 };
 
@@ -179,7 +181,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
         mbar_wait(&tempty[acc], acc_ph, wctx);
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * Cfg::BN;
+        const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
         for (int kb = 0; kb < kb_count; ++kb) {
           mbar_wait(&full[s], ph, wctx);
           tc_fence_after();
@@ -219,7 +221,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = (r % nt) * Cfg::BN;
       mbar_wait(&tfull[acc], acc_ph, wctx);
       tc_fence_after();
-      const uint32_t t_acc = tmem_addr(tmem_base, lane_base, acc * Cfg::BN);
+      const uint32_t t_acc = tmem_addr(tmem_base, lane_base, acc * Cfg::ACC_STRIDE);
       const int m = m0 + lane_base + lane;
       if constexpr (!Epi::kPaired) {
 #pragma unroll 1

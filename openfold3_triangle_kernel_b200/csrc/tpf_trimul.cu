@@ -1,0 +1,765 @@
+// Triangle multiplicative update (outgoing / incoming), forward and backward, for sm_100a.
+//
+//   zn  = LayerNorm_in(z)                                  a = (zn Wap^T) * sigmoid(zn Wag^T) * mask
+//   x[i,j,c] = sum_k a[i,k,c] b[j,k,c]   (outgoing)        b = (zn Wbp^T) * sigmoid(zn Wbg^T) * mask
+//   x[i,j,c] = sum_k a[k,i,c] b[k,j,c]   (incoming)        out = (LayerNorm_out(x) Wz^T) * sigmoid(zn Wg^T)
+//
+// Stands in for the reference's native TriMul stages and the cuBLAS calls between them
+// (openfold3/core/kernels/turbopairformer/turbopairformer_trimul_cuda.cu:634-1047, 1202-1470,
+//  1541-1809, 226-438 and turbopairformer_trimul.py:184-392).  Rounding points follow the
+// reference: fp32 master weights are rounded to bf16 once, LayerNorm statistics are fp32 with
+// var = E[x^2] - mean^2 and eps = 1e-5, intermediates (zn, a, b, gate logits, x) are bf16,
+// weight gradients are fp32 sums folded in a fixed order.
+//
+// Every GEMM-shaped stage runs on the tcgen05 engine of tpf_gemm.cuh; gating, masking and the
+// channel-major re-layout that the k-contraction wants are fused into GEMM epilogues.  The
+// a / b / x tensors live channel-major ([B*C][N*N]) so that the k-contraction is a plain batched
+// GEMM in both directions (K-major operands when outgoing, MN-major when incoming).
+#include "tpf_gemm_host.cuh"
+
+namespace tpf {
+
+static __device__ int g_trimul_status;
+
+int trimul_status_fetch_and_clear(int* out) {
+  int v = 0, zero = 0;
+  TPF_CUDA_OK(cudaMemcpyFromSymbol(&v, g_trimul_status, sizeof(int)));
+  if (v) TPF_CUDA_OK(cudaMemcpyToSymbol(g_trimul_status, &zero, sizeof(int)));
+  *out = v;
+  return TPF_OK;
+}
+
+int bmm_bf16(const void* A, int64_t lda, int64_t bsa, int a_mn, const void* B, int64_t ldb, int64_t bsb, int b_mn,
+             void* D, int64_t ldd, int64_t bsd, int out_f32, int64_t M, int64_t N, int64_t K, int64_t batch,
+             int64_t k_per_split, int swizzle_bytes, cudaStream_t stream);
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
+
+// =============================================================================================
+// weight packing: fp32 masters -> bf16 W5 [5C,C] = [a_p; a_g; b_p; b_g; g], W5T [C,5C], Wz [C,C], WzT [C,C]
+// =============================================================================================
+__global__ void trimul_pack_weights_kernel(const float* __restrict__ p_in, const float* __restrict__ g_in,
+                                           const float* __restrict__ p_out, const float* __restrict__ g_out,
+                                           bf16* __restrict__ W5, bf16* __restrict__ W5T, bf16* __restrict__ Wz,
+                                           bf16* __restrict__ WzT, int C) {
+  const int n = 5 * C * C;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int row = i / C, col = i % C;
+    const int blk = row / C, r = row % C;
+    float v;
+    if (blk == 0) v = p_in[r * C + col];
+    else if (blk == 1) v = g_in[r * C + col];
+    else if (blk == 2) v = p_in[(C + r) * C + col];
+    else if (blk == 3) v = g_in[(C + r) * C + col];
+    else v = g_out[r * C + col];
+    const bf16 h = __float2bfloat16(v);
+    W5[i] = h;
+    W5T[col * 5 * C + row] = h;
+    if (i < C * C) {
+      const bf16 hz = __float2bfloat16(p_out[i]);
+      Wz[i] = hz;
+      WzT[col * C + row] = hz;
+    }
+  }
+}
+
+// =============================================================================================
+// LayerNorm over the last dim of a row-major [R,C] bf16 tensor (input norm), forward
+// =============================================================================================
+template <int C>
+struct RowLanes {
+  static constexpr int LPR = C / 4;                 // lanes per row, 4 channels each
+  static constexpr int RPW = 32 / LPR;              // rows per warp (1 when C = 96)
+  static constexpr int RED = (C == 96) ? 32 : LPR;  // shuffle-reduction width
+};
+
+template <int C>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int off = RowLanes<C>::RED / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+template <int C>
+__global__ void __launch_bounds__(256) trimul_ln_fwd_kernel(const bf16* __restrict__ z, const float* __restrict__ gamma,
+                                                            const float* __restrict__ beta, bf16* __restrict__ zln,
+                                                            float* __restrict__ mean, float* __restrict__ rstd,
+                                                            int64_t R) {
+  using L = RowLanes<C>;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int sub = lane / L::LPR, part = lane % L::LPR;
+  const int64_t row = warp * L::RPW + sub;
+  const bool active = sub < L::RPW && row < R;
+  float x[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    const uint2 u = *reinterpret_cast<const uint2*>(z + row * C + part * 4);
+    x[0] = bf16_lo(u.x); x[1] = bf16_hi(u.x); x[2] = bf16_lo(u.y); x[3] = bf16_hi(u.y);
+  }
+  const float s1 = group_sum<C>(x[0] + x[1] + x[2] + x[3]);
+  const float s2 = group_sum<C>(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+  const float mu = s1 * (1.f / C);
+  const float var = fmaxf(s2 * (1.f / C) - mu * mu, 0.f);
+  const float rs = rsqrtf(var + 1e-5f);
+  if (active) {
+    const float4 g = *reinterpret_cast<const float4*>(gamma + part * 4);
+    const float4 b = *reinterpret_cast<const float4*>(beta + part * 4);
+    uint2 o;
+    o.x = pack_bf16x2((x[0] - mu) * rs * g.x + b.x, (x[1] - mu) * rs * g.y + b.y);
+    o.y = pack_bf16x2((x[2] - mu) * rs * g.z + b.z, (x[3] - mu) * rs * g.w + b.w);
+    *reinterpret_cast<uint2*>(zln + row * C + part * 4) = o;
+    if (part == 0) {
+      mean[row] = mu;
+      rstd[row] = rs;
+    }
+  }
+}
+
+// =============================================================================================
+// Output norm forward: channel-major x [B*C][NN] -> row-major LayerNorm(x) [R,C] + mean/rstd
+// =============================================================================================
+template <int C>
+__global__ void __launch_bounds__(256) trimul_xnorm_fwd_kernel(const bf16* __restrict__ x_cm,
+                                                               const float* __restrict__ gamma,
+                                                               const float* __restrict__ beta, bf16* __restrict__ xln,
+                                                               float* __restrict__ mean, float* __restrict__ rstd,
+                                                               int64_t NN, int tiles_per_batch) {
+  __shared__ float tile[C][65];
+  const int bb = blockIdx.x / tiles_per_batch;
+  const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * 64;
+  for (int idx = threadIdx.x; idx < C * 64; idx += 256) {
+    const int c = idx >> 6, j = idx & 63;
+    tile[c][j] = (r0 + j < NN) ? __bfloat162float(x_cm[((int64_t)bb * C + c) * NN + r0 + j]) : 0.f;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int j = warp; j < 64; j += 8) {
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = lane; c < C; c += 32) {
+      const float v = tile[c][j];
+      s1 += v;
+      s2 += v * v;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, off);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, off);
+    }
+    const float mu = s1 * (1.f / C);
+    const float rs = rsqrtf(fmaxf(s2 * (1.f / C) - mu * mu, 0.f) + 1e-5f);
+    if (r0 + j < NN) {
+      const int64_t row = (int64_t)bb * NN + r0 + j;
+#pragma unroll
+      for (int c = lane; c < C; c += 32)
+        xln[row * C + c] = __float2bfloat16((tile[c][j] - mu) * rs * gamma[c] + beta[c]);
+      if (lane == 0) {
+        mean[row] = mu;
+        rstd[row] = rs;
+      }
+    }
+  }
+}
+
+// =============================================================================================
+// GEMM epilogues
+// =============================================================================================
+// Projection + gating.  GEMM N axis = [a_p | a_g] [b_p | b_g] [g | pad], one tile of width 2C each.
+struct EpiProjGate {
+  struct Params {
+    bf16* a_cm;        // [B*C][NN]
+    bf16* b_cm;        // [B*C][NN]
+    bf16* gate;        // [R][C] raw gate logits
+    const float* mask; // [R]
+    int C;
+    int64_t NN;
+  };
+  static constexpr bool kPaired = true;
+  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
+                                                const float (&v0)[32], const float (&v1)[32]) {
+    if (m >= sh.M) return;
+    const int which = n0 / (2 * p.C);
+    if (which == 2) {
+      bf16* row = p.gate + (int64_t)m * p.C + c0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 u;
+        u.x = pack_bf16x2(v0[8 * i + 0], v0[8 * i + 1]);
+        u.y = pack_bf16x2(v0[8 * i + 2], v0[8 * i + 3]);
+        u.z = pack_bf16x2(v0[8 * i + 4], v0[8 * i + 5]);
+        u.w = pack_bf16x2(v0[8 * i + 6], v0[8 * i + 7]);
+        reinterpret_cast<uint4*>(row)[i] = u;
+      }
+      return;
+    }
+    const float mk = p.mask[m];
+    const int64_t bb = m / p.NN, rr = m - bb * p.NN;
+    bf16* dst = (which == 0 ? p.a_cm : p.b_cm) + (bb * p.C + c0) * p.NN + rr;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) dst[(int64_t)i * p.NN] = __float2bfloat16(v0[i] * sigmoid_fast(v1[i]) * mk);
+  }
+};
+
+// Output projection: out = acc * sigmoid(gate)
+struct EpiOutGate {
+  struct Params {
+    bf16* out;        // [R][C]
+    const bf16* gate; // [R][C]
+    int C;
+  };
+  static constexpr bool kPaired = false;
+  __device__ static __forceinline__ void apply(const Params& p, const GemmShape& sh, int, int m, int n0,
+                                               const float (&v)[32]) {
+    if (m >= sh.M) return;
+    const bf16* g = p.gate + (int64_t)m * p.C + n0;
+    bf16* o = p.out + (int64_t)m * p.C + n0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 gu = reinterpret_cast<const uint4*>(g)[i];
+      const uint32_t gw[4] = {gu.x, gu.y, gu.z, gu.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        ow[e] = pack_bf16x2(v[8 * i + 2 * e] * sigmoid_fast(bf16_lo(gw[e])),
+                            v[8 * i + 2 * e + 1] * sigmoid_fast(bf16_hi(gw[e])));
+      reinterpret_cast<uint4*>(o)[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  }
+};
+
+// Backward of the gated projections: recomputed (p, g) pair + incoming d_a / d_b -> d_proj5[:, 0:4C]
+struct EpiGateSplitBwd {
+  struct Params {
+    const bf16* da_cm;  // [B*C][NN]
+    const bf16* db_cm;
+    const float* mask;  // [R]
+    bf16* d_proj5;      // [R][5C]
+    int C;
+    int64_t NN;
+  };
+  static constexpr bool kPaired = true;
+  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
+                                                const float (&v0)[32], const float (&v1)[32]) {
+    if (m >= sh.M) return;
+    const int which = n0 / (2 * p.C);  // 0: a, 1: b
+    const float mk = p.mask[m];
+    const int64_t bb = m / p.NN, rr = m - bb * p.NN;
+    const bf16* src = (which == 0 ? p.da_cm : p.db_cm) + (bb * p.C + c0) * p.NN + rr;
+    bf16* dp = p.d_proj5 + (int64_t)m * 5 * p.C + which * 2 * p.C + c0;  // d_p block
+    bf16* dg = dp + p.C;                                                // d_g block
+    float o0[32], o1[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float d = __bfloat162float(src[(int64_t)i * p.NN]) * mk;
+      const float s = sigmoid_fast(v1[i]);
+      o0[i] = d * s;
+      o1[i] = d * v0[i] * s * (1.f - s);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 u, w;
+      u.x = pack_bf16x2(o0[8 * i + 0], o0[8 * i + 1]); u.y = pack_bf16x2(o0[8 * i + 2], o0[8 * i + 3]);
+      u.z = pack_bf16x2(o0[8 * i + 4], o0[8 * i + 5]); u.w = pack_bf16x2(o0[8 * i + 6], o0[8 * i + 7]);
+      w.x = pack_bf16x2(o1[8 * i + 0], o1[8 * i + 1]); w.y = pack_bf16x2(o1[8 * i + 2], o1[8 * i + 3]);
+      w.z = pack_bf16x2(o1[8 * i + 4], o1[8 * i + 5]); w.w = pack_bf16x2(o1[8 * i + 6], o1[8 * i + 7]);
+      reinterpret_cast<uint4*>(dp)[i] = u;
+      reinterpret_cast<uint4*>(dg)[i] = w;
+    }
+  }
+};
+
+// =============================================================================================
+// backward elementwise stages
+// =============================================================================================
+// d_y = d_out * sigmoid(g);  d_glogit = d_out * out * (1 - sigmoid(g))  -> d_proj5[:, 4C:5C]
+__global__ void __launch_bounds__(256) trimul_out_gate_bwd_kernel(const bf16* __restrict__ d_out,
+                                                                  const bf16* __restrict__ out,
+                                                                  const bf16* __restrict__ gate, bf16* __restrict__ d_y,
+                                                                  bf16* __restrict__ d_proj5, int64_t R, int C) {
+  const int64_t n8 = R * C / 8;
+  const int per_row = C / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 a = reinterpret_cast<const uint4*>(d_out)[i];
+    const uint4 b = reinterpret_cast<const uint4*>(out)[i];
+    const uint4 g = reinterpret_cast<const uint4*>(gate)[i];
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    uint32_t y[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float s0 = sigmoid_fast(bf16_lo(gw[e])), s1 = sigmoid_fast(bf16_hi(gw[e]));
+      const float d0 = bf16_lo(aw[e]), d1 = bf16_hi(aw[e]);
+      y[e] = pack_bf16x2(d0 * s0, d1 * s1);
+      l[e] = pack_bf16x2(d0 * bf16_lo(bw[e]) * (1.f - s0), d1 * bf16_hi(bw[e]) * (1.f - s1));
+    }
+    reinterpret_cast<uint4*>(d_y)[i] = make_uint4(y[0], y[1], y[2], y[3]);
+    const int64_t row = i / per_row;
+    const int col8 = (int)(i % per_row);
+    *reinterpret_cast<uint4*>(d_proj5 + row * 5 * C + 4 * C + col8 * 8) = make_uint4(l[0], l[1], l[2], l[3]);
+  }
+}
+
+// Output-norm backward.  d_xln row-major [R,C], x channel-major -> d_x channel-major; per-block
+// partial sums for d_gamma / d_beta (fixed order inside the block, folded in block order later).
+template <int C>
+__global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __restrict__ d_xln,
+                                                               const bf16* __restrict__ x_cm,
+                                                               const float* __restrict__ gamma,
+                                                               const float* __restrict__ mean,
+                                                               const float* __restrict__ rstd, bf16* __restrict__ dx_cm,
+                                                               float* __restrict__ partials, int64_t NN,
+                                                               int tiles_per_batch) {
+  extern __shared__ float sm[];
+  float(*xh)[65] = reinterpret_cast<float(*)[65]>(sm);            // xhat [C][65]
+  float(*dg)[65] = reinterpret_cast<float(*)[65]>(sm + C * 65);   // d_xln [C][65]
+  __shared__ float s_m1[64], s_m2[64], s_rs[64];
+  const int bb = blockIdx.x / tiles_per_batch;
+  const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * 64;
+  for (int idx = threadIdx.x; idx < C * 64; idx += 256) {
+    const int c = idx >> 6, j = idx & 63;
+    float v = 0.f;
+    if (r0 + j < NN) {
+      const int64_t row = (int64_t)bb * NN + r0 + j;
+      v = (__bfloat162float(x_cm[((int64_t)bb * C + c) * NN + r0 + j]) - mean[row]) * rstd[row];
+    }
+    xh[c][j] = v;
+  }
+  for (int idx = threadIdx.x; idx < C * 64; idx += 256) {
+    const int j = idx / C, c = idx % C;
+    dg[c][j] = (r0 + j < NN) ? __bfloat162float(d_xln[((int64_t)bb * NN + r0 + j) * C + c]) : 0.f;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int j = warp; j < 64; j += 8) {
+    float a1 = 0.f, a2 = 0.f;
+#pragma unroll
+    for (int c = lane; c < C; c += 32) {
+      const float g = gamma[c] * dg[c][j];
+      a1 += g;
+      a2 += g * xh[c][j];
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      a1 += __shfl_xor_sync(0xffffffffu, a1, off);
+      a2 += __shfl_xor_sync(0xffffffffu, a2, off);
+    }
+    if (lane == 0) {
+      s_m1[j] = a1 * (1.f / C);
+      s_m2[j] = a2 * (1.f / C);
+      s_rs[j] = (r0 + j < NN) ? rstd[(int64_t)bb * NN + r0 + j] : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < C * 64; idx += 256) {
+    const int c = idx >> 6, j = idx & 63;
+    if (r0 + j < NN)
+      dx_cm[((int64_t)bb * C + c) * NN + r0 + j] =
+          __float2bfloat16(s_rs[j] * (gamma[c] * dg[c][j] - s_m1[j] - xh[c][j] * s_m2[j]));
+  }
+  if (threadIdx.x < C) {
+    const int c = threadIdx.x;
+    float sg = 0.f, sb = 0.f;
+    for (int j = 0; j < 64; ++j) {
+      sg += dg[c][j] * xh[c][j];
+      sb += dg[c][j];
+    }
+    partials[(int64_t)blockIdx.x * 2 * C + c] = sg;
+    partials[(int64_t)blockIdx.x * 2 * C + C + c] = sb;
+  }
+}
+
+// Input-norm backward, row-major.  d_z = rstd (gamma d_zln - mean(gamma d_zln) - xhat mean(gamma d_zln xhat))
+template <int C>
+__global__ void __launch_bounds__(256) trimul_ln_bwd_kernel(const bf16* __restrict__ d_zln, const bf16* __restrict__ z,
+                                                            const float* __restrict__ gamma,
+                                                            const float* __restrict__ mean,
+                                                            const float* __restrict__ rstd, bf16* __restrict__ d_z,
+                                                            float* __restrict__ partials, int64_t R,
+                                                            int rows_per_block) {
+  using L = RowLanes<C>;
+  __shared__ float red[8][2][C];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / L::LPR, part = lane % L::LPR;
+  const int64_t row_begin = (int64_t)blockIdx.x * rows_per_block;
+  float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (sub < L::RPW) g4 = *reinterpret_cast<const float4*>(gamma + part * 4);
+  float ag[4] = {0.f, 0.f, 0.f, 0.f}, ab[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int it = warp * L::RPW; it < rows_per_block; it += 8 * L::RPW) {
+    const int64_t row = row_begin + it + sub;
+    const bool active = sub < L::RPW && it + sub < rows_per_block && row < R;
+    float d[4] = {0.f, 0.f, 0.f, 0.f}, xh[4] = {0.f, 0.f, 0.f, 0.f};
+    float rs = 0.f;
+    if (active) {
+      const uint2 du = *reinterpret_cast<const uint2*>(d_zln + row * C + part * 4);
+      const uint2 zu = *reinterpret_cast<const uint2*>(z + row * C + part * 4);
+      const float mu = mean[row];
+      rs = rstd[row];
+      d[0] = bf16_lo(du.x); d[1] = bf16_hi(du.x); d[2] = bf16_lo(du.y); d[3] = bf16_hi(du.y);
+      xh[0] = (bf16_lo(zu.x) - mu) * rs; xh[1] = (bf16_hi(zu.x) - mu) * rs;
+      xh[2] = (bf16_lo(zu.y) - mu) * rs; xh[3] = (bf16_hi(zu.y) - mu) * rs;
+    }
+    const float gd[4] = {g4.x * d[0], g4.y * d[1], g4.z * d[2], g4.w * d[3]};
+    const float m1 = group_sum<C>(gd[0] + gd[1] + gd[2] + gd[3]) * (1.f / C);
+    const float m2 = group_sum<C>(gd[0] * xh[0] + gd[1] * xh[1] + gd[2] * xh[2] + gd[3] * xh[3]) * (1.f / C);
+    if (active) {
+      uint2 o;
+      o.x = pack_bf16x2(rs * (gd[0] - m1 - xh[0] * m2), rs * (gd[1] - m1 - xh[1] * m2));
+      o.y = pack_bf16x2(rs * (gd[2] - m1 - xh[2] * m2), rs * (gd[3] - m1 - xh[3] * m2));
+      *reinterpret_cast<uint2*>(d_z + row * C + part * 4) = o;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ag[e] += d[e] * xh[e];
+        ab[e] += d[e];
+      }
+    }
+  }
+  // fixed-order fold: rows of a warp that share channels (sub = 0..RPW-1), then the 8 warps
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float vg = ag[e], vb = ab[e];
+    for (int s = 1; s < L::RPW; ++s) {
+      const float og = __shfl_sync(0xffffffffu, ag[e], (lane % L::LPR) + s * L::LPR);
+      const float ob = __shfl_sync(0xffffffffu, ab[e], (lane % L::LPR) + s * L::LPR);
+      vg += og;
+      vb += ob;
+    }
+    if (sub == 0 && part * 4 + e < C) {
+      red[warp][0][part * 4 + e] = vg;
+      red[warp][1][part * 4 + e] = vb;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 2 * C) {
+    const int which = threadIdx.x / C, c = threadIdx.x % C;
+    float s = red[0][which][c];
+    for (int w = 1; w < 8; ++w) s += red[w][which][c];
+    partials[(int64_t)blockIdx.x * 2 * C + which * C + c] = s;
+  }
+}
+
+// out[j] = sum over blocks (ascending) of partials[blk][j], j < width
+__global__ void __launch_bounds__(256) trimul_colsum_fold_kernel(const float* __restrict__ partials, int n_blocks,
+                                                                 int width, float* __restrict__ out_a,
+                                                                 float* __restrict__ out_b, int half) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= width) return;
+  float s = 0.f;
+  for (int b = 0; b < n_blocks; ++b) s = __fadd_rn(s, partials[(int64_t)b * width + j]);
+  if (j < half) out_a[j] = s;
+  else out_b[j - half] = s;
+}
+
+// Weight-gradient fold: out_row_block[r][c] = sum over splits (ascending) of part[s][m][c].
+// Rows are routed in blocks of C rows to up to five destinations (W5 = [a_p; a_g; b_p; b_g; g]).
+struct WgradDst {
+  float* dst[5];
+};
+__global__ void __launch_bounds__(256) trimul_wgrad_fold_kernel(const float* __restrict__ part, int n_splits, int M,
+                                                                int C, WgradDst d) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * C) return;
+  float s = 0.f;
+  for (int k = 0; k < n_splits; ++k) s = __fadd_rn(s, part[(int64_t)k * M * C + i]);
+  const int row = i / C, col = i % C;
+  d.dst[row / C][(row % C) * C + col] = s;
+}
+
+// =============================================================================================
+// host orchestration
+// =============================================================================================
+struct TrimulPacked {
+  bf16 *W5, *W5T, *Wz, *WzT;
+};
+static int64_t packed_weight_elems(int64_t C) { return 12 * C * C; }
+
+static int pack_weights(const float* p_in, const float* g_in, const float* p_out, const float* g_out, void* buf,
+                        int C, TrimulPacked* pk, cudaStream_t stream) {
+  bf16* base = reinterpret_cast<bf16*>(buf);
+  pk->W5 = base;
+  pk->W5T = base + 5 * C * C;
+  pk->Wz = base + 10 * C * C;
+  pk->WzT = base + 11 * C * C;
+  trimul_pack_weights_kernel<<<64, 256, 0, stream>>>(p_in, g_in, p_out, g_out, pk->W5, pk->W5T, pk->Wz, pk->WzT, C);
+  TPF_CUDA_OK(cudaGetLastError());
+  return TPF_OK;
+}
+
+template <int C, class Epi>
+static int proj_gemm(const bf16* zln, const bf16* W5, int64_t R, int n_cols, const typename Epi::Params& ep,
+                     int* status, cudaStream_t stream) {
+  using Cfg = GemmCfg<128, 2 * C, 128, false, 128, false, 4>;
+  GemmShape sh{(int)R, n_cols, C, 1, 0};
+  return launch_gemm<Cfg, Epi>(zln, C, 0, W5, C, 0, sh, ep, status, stream);
+}
+
+template <int C>
+static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk, const float* gin, const float* bin,
+                        const float* gout, const float* bout, int incoming, int64_t B, int64_t N, bf16* out, bf16* zln,
+                        float* mean_in, float* rstd_in, bf16* a_cm, bf16* b_cm, bf16* gate, bf16* x_cm, bf16* xln,
+                        float* mean_out, float* rstd_out, int* status, cudaStream_t stream) {
+  const int64_t NN = N * N, R = B * NN;
+  using L = RowLanes<C>;
+  {
+    const int64_t warps = (R + L::RPW - 1) / L::RPW;
+    const int64_t blocks = (warps + 7) / 8;
+    trimul_ln_fwd_kernel<C><<<(unsigned)blocks, 256, 0, stream>>>(z, gin, bin, zln, mean_in, rstd_in, R);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+  int rc;
+  {
+    EpiProjGate::Params ep{a_cm, b_cm, gate, mask, C, NN};
+    if ((rc = proj_gemm<C, EpiProjGate>(zln, pk.W5, R, 5 * C, ep, status, stream))) return rc;
+  }
+  // k-contraction: batch = B*C problems of N x N x N
+  rc = bmm_bf16(a_cm, N, NN, incoming, b_cm, N, NN, incoming, x_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream);
+  if (rc) return rc;
+  {
+    const int tiles = (int)((NN + 63) / 64);
+    trimul_xnorm_fwd_kernel<C><<<(unsigned)(B * tiles), 256, 0, stream>>>(x_cm, gout, bout, xln, mean_out, rstd_out,
+                                                                          NN, tiles);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+  {
+    using Cfg = GemmCfg<128, C, 128, false, 128, false, 4>;
+    GemmShape sh{(int)R, C, C, 1, 0};
+    EpiOutGate::Params ep{out, gate, C};
+    if ((rc = launch_gemm<Cfg, EpiOutGate>(xln, C, 0, pk.Wz, C, 0, sh, ep, status, stream))) return rc;
+  }
+  return TPF_OK;
+}
+
+static void split_plan(int64_t R, int tiles_mn, int* n_splits, int64_t* k_per_split) {
+  int64_t s = sm_count() / (tiles_mn > 0 ? tiles_mn : 1);
+  if (s < 1) s = 1;
+  int64_t kps = ((R + s - 1) / s + 63) / 64 * 64;
+  if (kps < 64) kps = 64;
+  *k_per_split = kps;
+  *n_splits = (int)((R + kps - 1) / kps);
+}
+
+struct TrimulBwdWorkspace {
+  bf16 *wpack, *d_y, *d_proj5, *d_xln, *dx_cm, *da_cm, *db_cm;  // d_zln aliases d_xln
+  float *part_w5, *part_wz, *part_ln_out, *part_ln_in;
+  int splits_w5, splits_wz, blocks_ln_out, blocks_ln_in, rows_per_block_in;
+  int64_t kps_w5, kps_wz;
+  int64_t total_bytes;
+};
+
+static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
+
+static void plan_bwd_workspace(int64_t B, int64_t N, int64_t C, char* base, TrimulBwdWorkspace* w) {
+  const int64_t NN = N * N, R = B * NN;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    char* p = base ? base + off : nullptr;
+    off += align256(bytes);
+    return p;
+  };
+  w->wpack = reinterpret_cast<bf16*>(take(packed_weight_elems(C) * 2));
+  w->d_y = reinterpret_cast<bf16*>(take(R * C * 2));
+  w->d_proj5 = reinterpret_cast<bf16*>(take(R * 5 * C * 2));
+  w->d_xln = reinterpret_cast<bf16*>(take(R * C * 2));
+  w->dx_cm = reinterpret_cast<bf16*>(take(R * C * 2));
+  w->da_cm = reinterpret_cast<bf16*>(take(R * C * 2));
+  w->db_cm = reinterpret_cast<bf16*>(take(R * C * 2));
+  split_plan(R, (int)((5 * C + 127) / 128), &w->splits_w5, &w->kps_w5);
+  split_plan(R, 1, &w->splits_wz, &w->kps_wz);
+  w->part_w5 = reinterpret_cast<float*>(take((int64_t)w->splits_w5 * 5 * C * C * 4));
+  w->part_wz = reinterpret_cast<float*>(take((int64_t)w->splits_wz * C * C * 4));
+  w->blocks_ln_out = (int)(B * ((NN + 63) / 64));
+  w->rows_per_block_in = 256;
+  w->blocks_ln_in = (int)((R + 255) / 256);
+  w->part_ln_out = reinterpret_cast<float*>(take((int64_t)w->blocks_ln_out * 2 * C * 4));
+  w->part_ln_in = reinterpret_cast<float*>(take((int64_t)w->blocks_ln_in * 2 * C * 4));
+  w->total_bytes = off;
+}
+
+template <int C>
+static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, const float* p_in, const float* g_in,
+                        const float* p_out, const float* g_out, const float* gin, const float* gout, int incoming,
+                        int64_t B, int64_t N, const bf16* out, const bf16* zln, const float* mean_in,
+                        const float* rstd_in, const bf16* a_cm, const bf16* b_cm, const bf16* gate, const bf16* x_cm,
+                        const bf16* xln, const float* mean_out, const float* rstd_out, bf16* d_z, float* d_p_in,
+                        float* d_g_in, float* d_p_out, float* d_g_out, float* d_gin, float* d_bin, float* d_gout,
+                        float* d_bout, char* workspace, int* status, cudaStream_t stream) {
+  const int64_t NN = N * N, R = B * NN;
+  TrimulBwdWorkspace w;
+  plan_bwd_workspace(B, N, C, workspace, &w);
+  TrimulPacked pk;
+  int rc;
+  if ((rc = pack_weights(p_in, g_in, p_out, g_out, w.wpack, C, &pk, stream))) return rc;
+
+  // 1. output gate: d_y, d_glogit
+  {
+    int blocks = (int)((R * C / 8 + 255) / 256);
+    if (blocks > 16 * sm_count()) blocks = 16 * sm_count();
+    trimul_out_gate_bwd_kernel<<<blocks, 256, 0, stream>>>(d_out, out, gate, w.d_y, w.d_proj5, R, C);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+  // 2. d_xln = d_y Wz ; d_wz = d_y^T xln
+  {
+    using Cfg = GemmCfg<128, 128, 128, false, 128, false, 4>;
+    using Epi = EpiStore<bf16>;
+    GemmShape sh{(int)R, C, C, 1, 0};
+    typename Epi::Params ep{w.d_xln, C, 0};
+    if ((rc = launch_gemm<Cfg, Epi>(w.d_y, C, 0, pk.WzT, C, 0, sh, ep, status, stream))) return rc;
+  }
+  rc = bmm_bf16(w.d_y, C, 0, 1, xln, C, 0, 1, w.part_wz, C, (int64_t)C * C, 1, C, C, R, w.splits_wz, w.kps_wz, 128,
+                stream);
+  if (rc) return rc;
+  {
+    WgradDst d;
+    for (int i = 0; i < 5; ++i) d.dst[i] = d_p_out;
+    trimul_wgrad_fold_kernel<<<(C * C + 255) / 256, 256, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+  // 3. output norm backward -> d_x (channel-major), d_gamma_out, d_beta_out
+  {
+    const int tiles = (int)((NN + 63) / 64);
+    auto kern = trimul_xnorm_bwd_kernel<C>;
+    const int smem = 2 * C * 65 * 4;
+    static bool attr_done = false;
+    if (!attr_done) {
+      TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr_done = true;
+    }
+    kern<<<(unsigned)(B * tiles), 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out,
+                                                       NN, tiles);
+    TPF_CUDA_OK(cudaGetLastError());
+    trimul_colsum_fold_kernel<<<(2 * C + 255) / 256, 256, 0, stream>>>(w.part_ln_out, w.blocks_ln_out, 2 * C, d_gout,
+                                                                       d_bout, C);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+  // 4. contraction backward
+  if (!incoming) {
+    // d_a[c,i,k] = sum_j d_x[c,i,j] b[c,j,k] ; d_b[c,j,k] = sum_i d_x[c,i,j] a[c,i,k]
+    if ((rc = bmm_bf16(w.dx_cm, N, NN, 0, b_cm, N, NN, 1, w.da_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream))) return rc;
+    if ((rc = bmm_bf16(w.dx_cm, N, NN, 1, a_cm, N, NN, 1, w.db_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream))) return rc;
+  } else {
+    // d_a[c,k,i] = sum_j b[c,k,j] d_x[c,i,j] ; d_b[c,k,j] = sum_i a[c,k,i] d_x[c,i,j]
+    if ((rc = bmm_bf16(b_cm, N, NN, 0, w.dx_cm, N, NN, 0, w.da_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream))) return rc;
+    if ((rc = bmm_bf16(a_cm, N, NN, 0, w.dx_cm, N, NN, 1, w.db_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream))) return rc;
+  }
+  // 5. gated projections backward (recompute p, g) -> d_proj5[:, 0:4C]
+  {
+    EpiGateSplitBwd::Params ep{w.da_cm, w.db_cm, mask, w.d_proj5, C, NN};
+    if ((rc = proj_gemm<C, EpiGateSplitBwd>(zln, pk.W5, R, 4 * C, ep, status, stream))) return rc;
+  }
+  // 6. d_zln = d_proj5 W5 ; dW5 = d_proj5^T zln
+  bf16* d_zln = w.d_xln;
+  {
+    using Cfg = GemmCfg<128, 128, 128, false, 128, false, 4>;
+    using Epi = EpiStore<bf16>;
+    GemmShape sh{(int)R, C, 5 * C, 1, 0};
+    typename Epi::Params ep{d_zln, C, 0};
+    if ((rc = launch_gemm<Cfg, Epi>(w.d_proj5, 5 * C, 0, pk.W5T, 5 * C, 0, sh, ep, status, stream))) return rc;
+  }
+  rc = bmm_bf16(w.d_proj5, 5 * C, 0, 1, zln, C, 0, 1, w.part_w5, C, (int64_t)5 * C * C, 1, 5 * C, C, R, w.splits_w5,
+                w.kps_w5, 128, stream);
+  if (rc) return rc;
+  {
+    WgradDst d;
+    d.dst[0] = d_p_in;              // a_p
+    d.dst[1] = d_g_in;              // a_g
+    d.dst[2] = d_p_in + C * C;      // b_p
+    d.dst[3] = d_g_in + C * C;      // b_g
+    d.dst[4] = d_g_out;             // g
+    trimul_wgrad_fold_kernel<<<(5 * C * C + 255) / 256, 256, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+  // 7. input norm backward
+  {
+    trimul_ln_bwd_kernel<C><<<w.blocks_ln_in, 256, 0, stream>>>(d_zln, z, gin, mean_in, rstd_in, d_z, w.part_ln_in, R,
+                                                                w.rows_per_block_in);
+    TPF_CUDA_OK(cudaGetLastError());
+    trimul_colsum_fold_kernel<<<(2 * C + 255) / 256, 256, 0, stream>>>(w.part_ln_in, w.blocks_ln_in, 2 * C, d_gin,
+                                                                       d_bin, C);
+    TPF_CUDA_OK(cudaGetLastError());
+  }
+  return TPF_OK;
+}
+
+static int check_trimul_shape(const char* who, int64_t B, int64_t N, int64_t C) {
+  TPF_REQUIRE(B > 0 && N > 0, TPF_ERR_INVALID_ARGUMENT, "%s: B and N must be positive", who);
+  TPF_REQUIRE(C == 32 || C == 64 || C == 96 || C == 128, TPF_ERR_UNSUPPORTED, "%s: C=%lld not in {32,64,96,128}", who,
+              (long long)C);
+  TPF_REQUIRE(N % 8 == 0, TPF_ERR_UNSUPPORTED, "%s: N=%lld must be a multiple of 8 (pad on the host side)", who,
+              (long long)N);
+  TPF_REQUIRE(B * N * N < (1ll << 31), TPF_ERR_INVALID_ARGUMENT, "%s: B*N*N too large", who);
+  return TPF_OK;
+}
+
+int64_t trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C) { return align256(packed_weight_elems(C) * 2); }
+
+int64_t trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C) {
+  TrimulBwdWorkspace w;
+  plan_bwd_workspace(B, N, C, nullptr, &w);
+  return w.total_bytes;
+}
+
+int trimul_fwd(const void* z, const float* mask, const float* p_in, const float* g_in, const float* p_out,
+               const float* g_out, const float* gin, const float* bin, const float* gout, const float* bout,
+               int incoming, int64_t B, int64_t N, int64_t C, void* out, void* zln, float* mean_in, float* rstd_in,
+               void* a_cm, void* b_cm, void* gate, void* x_cm, void* xln, float* mean_out, float* rstd_out,
+               void* workspace, int64_t workspace_bytes, cudaStream_t stream) {
+  int rc = check_trimul_shape("trimul_fwd", B, N, C);
+  if (rc) return rc;
+  TPF_REQUIRE(z && mask && p_in && g_in && p_out && g_out && gin && bin && gout && bout && out && zln && mean_in &&
+                  rstd_in && a_cm && b_cm && gate && x_cm && xln && mean_out && rstd_out,
+              TPF_ERR_INVALID_ARGUMENT, "trimul_fwd: null pointer");
+  TPF_REQUIRE(workspace && workspace_bytes >= trimul_fwd_workspace_bytes(B, N, C), TPF_ERR_WORKSPACE,
+              "trimul_fwd: workspace of %lld bytes required", (long long)trimul_fwd_workspace_bytes(B, N, C));
+  int* status = nullptr;
+  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_trimul_status));
+  TrimulPacked pk;
+  if ((rc = pack_weights(p_in, g_in, p_out, g_out, workspace, (int)C, &pk, stream))) return rc;
+#define TPF_TRIMUL_FWD(CC)                                                                                         \
+  if (C == CC)                                                                                                     \
+    return trimul_fwd_t<CC>((const bf16*)z, mask, pk, gin, bin, gout, bout, incoming, B, N, (bf16*)out, (bf16*)zln, \
+                            mean_in, rstd_in, (bf16*)a_cm, (bf16*)b_cm, (bf16*)gate, (bf16*)x_cm, (bf16*)xln,       \
+                            mean_out, rstd_out, status, stream);
+  TPF_TRIMUL_FWD(32)
+  TPF_TRIMUL_FWD(64)
+  TPF_TRIMUL_FWD(96)
+  TPF_TRIMUL_FWD(128)
+#undef TPF_TRIMUL_FWD
+  return fail(TPF_ERR_UNSUPPORTED, "trimul_fwd: unsupported C");
+}
+
+int trimul_bwd(const void* d_out, const void* z, const float* mask, const float* p_in, const float* g_in,
+               const float* p_out, const float* g_out, const float* gin, const float* gout, int incoming, int64_t B,
+               int64_t N, int64_t C, const void* out, const void* zln, const float* mean_in, const float* rstd_in,
+               const void* a_cm, const void* b_cm, const void* gate, const void* x_cm, const void* xln,
+               const float* mean_out, const float* rstd_out, void* d_z, float* d_p_in, float* d_g_in, float* d_p_out,
+               float* d_g_out, float* d_gin, float* d_bin, float* d_gout, float* d_bout, void* workspace,
+               int64_t workspace_bytes, cudaStream_t stream) {
+  int rc = check_trimul_shape("trimul_bwd", B, N, C);
+  if (rc) return rc;
+  TPF_REQUIRE(d_out && z && mask && p_in && g_in && p_out && g_out && gin && gout && out && zln && mean_in &&
+                  rstd_in && a_cm && b_cm && gate && x_cm && xln && mean_out && rstd_out && d_z && d_p_in && d_g_in &&
+                  d_p_out && d_g_out && d_gin && d_bin && d_gout && d_bout,
+              TPF_ERR_INVALID_ARGUMENT, "trimul_bwd: null pointer");
+  TPF_REQUIRE(workspace && workspace_bytes >= trimul_bwd_workspace_bytes(B, N, C) &&
+                  (reinterpret_cast<uintptr_t>(workspace) & 255) == 0,
+              TPF_ERR_WORKSPACE, "trimul_bwd: 256-byte aligned workspace of %lld bytes required",
+              (long long)trimul_bwd_workspace_bytes(B, N, C));
+  int* status = nullptr;
+  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_trimul_status));
+#define TPF_TRIMUL_BWD(CC)                                                                                            \
+  if (C == CC)                                                                                                        \
+    return trimul_bwd_t<CC>((const bf16*)d_out, (const bf16*)z, mask, p_in, g_in, p_out, g_out, gin, gout, incoming,  \
+                            B, N, (const bf16*)out, (const bf16*)zln, mean_in, rstd_in, (const bf16*)a_cm,            \
+                            (const bf16*)b_cm, (const bf16*)gate, (const bf16*)x_cm, (const bf16*)xln, mean_out,      \
+                            rstd_out, (bf16*)d_z, d_p_in, d_g_in, d_p_out, d_g_out, d_gin, d_bin, d_gout, d_bout,     \
+                            (char*)workspace, status, stream);
+  TPF_TRIMUL_BWD(32)
+  TPF_TRIMUL_BWD(64)
+  TPF_TRIMUL_BWD(96)
+  TPF_TRIMUL_BWD(128)
+#undef TPF_TRIMUL_BWD
+  return fail(TPF_ERR_UNSUPPORTED, "trimul_bwd: unsupported C");
+}
+
+}  // namespace tpf
