@@ -43,6 +43,9 @@ const char* tpf_last_error_string(void);
  * cudaGetLastError (openfold3/core/kernels/turbopairformer/turbopairformer_triangle_forward.cu:1957). */
 int tpf_device_status(int* status);
 
+/* Kernel launches issued through this library by the calling process so far (host counter). */
+int64_t tpf_launch_count(void);
+
 /* Batched bf16 GEMM  D[b][m][n] = sum_k A[b][m][k] * B[b][n][k], fp32 accumulate.
  * a_mn / b_mn = 0: operand stored [batch][mn][k] (k contiguous);
  *             = 1: operand stored [batch][k][mn] (m or n contiguous).
@@ -86,6 +89,22 @@ int64_t tpf_attn_bwd_workspace_bytes(int64_t B, int64_t O, int64_t H, int64_t N,
  * (openfold3/core/kernels/turbopairformer/turbopairformer_triangle_delta.cu:343-414,
  *  openfold3/core/kernels/turbopairformer/turbopairformer_triangle_dq_dbias.cu:2526-2648) and the
  * Python workspace planner in turbopairformer_triangle_dq_dbias.py:466-669. */
+#define TPF_ATTN_BWD_STAGE_DELTA 1  /* delta = rowsum(dO * O) */
+#define TPF_ATTN_BWD_STAGE_DQKV 2   /* dq, dk, dv (reads delta) */
+#define TPF_ATTN_BWD_STAGE_DBIAS 4  /* dbias (reads delta) */
+#define TPF_ATTN_BWD_STAGE_ALL 7
+
+/* tpf_attn_bwd restricted to the stages in `stages` (bit mask above); used to time the
+ * stages separately.  tpf_attn_bwd(...) is tpf_attn_bwd_stages(..., TPF_ATTN_BWD_STAGE_ALL). */
+int tpf_attn_bwd_stages(const void* q, const void* k, const void* v, const void* d_out,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const void* out, const float* lse,
+                 const float* mask, int64_t mask_pitch,
+                 const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                 void* dq, void* dk, void* dv, float* dbias, float* delta,
+                 void* workspace, int64_t workspace_bytes,
+                 int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, int stages, void* stream);
+
 int tpf_attn_bwd(const void* q, const void* k, const void* v, const void* d_out,
                  const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                  const void* out, const float* lse,

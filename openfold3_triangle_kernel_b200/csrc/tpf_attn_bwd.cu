@@ -902,7 +902,7 @@ int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
     attr_done = true;
   }
   kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
-  TPF_CUDA_OK(cudaGetLastError());
+  TPF_LAUNCH_OK();
   return TPF_OK;
 }
 
@@ -921,7 +921,7 @@ int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out
                   const int64_t* k_strides, const int64_t* v_strides, const void* out, const float* lse,
                   const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
                   void* dq, void* dk, void* dv, float* delta, void* workspace, int64_t workspace_bytes, int64_t B,
-                  int64_t O, int64_t H, int64_t N, int64_t D, float scale, cudaStream_t stream) {
+                  int64_t O, int64_t H, int64_t N, int64_t D, float scale, int stages, cudaStream_t stream) {
   TPF_REQUIRE(q && k && v && d_out && out && lse && mask && bias && dq && dk && dv && delta, TPF_ERR_INVALID_ARGUMENT,
               "attn_bwd: null pointer");
   TPF_REQUIRE(B > 0 && O > 0 && H > 0 && N > 0, TPF_ERR_INVALID_ARGUMENT, "attn_bwd: B,O,H,N must be positive");
@@ -938,7 +938,7 @@ int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out
               "attn_bwd: workspace of %lld bytes required, %lld given", (long long)need, (long long)workspace_bytes);
 
   // delta = rowsum(dO * O)
-  {
+  if (stages & 1) {
     const int64_t rows = B * O * N * H;
     const int lanes = (int)D / 8;
     const int64_t threads = rows * lanes;
@@ -949,9 +949,10 @@ int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out
     if (D == 16) attn_delta_kernel<16><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
     else if (D == 32) attn_delta_kernel<32><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
     else attn_delta_kernel<64><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
 
+  if (!(stages & 2)) return TPF_OK;
   const int swz = 2 * (int)D;
   CUtensorMap tq, tk, tv, tdo, tb, tm;
   int rc;
@@ -999,7 +1000,7 @@ int launch_attn_dbias(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     attr_done = true;
   }
   kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
-  TPF_CUDA_OK(cudaGetLastError());
+  TPF_LAUNCH_OK();
   return TPF_OK;
 }
 
@@ -1070,7 +1071,7 @@ int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_ou
     int blocks = (int)((n + 255) / 256);
     if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
     attn_dbias_fold_kernel<<<blocks, 256, 0, stream>>>(p.part, dbias, n, n_chunks);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
   return TPF_OK;
 }

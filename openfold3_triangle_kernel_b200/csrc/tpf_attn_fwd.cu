@@ -512,7 +512,7 @@ int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
   int grid = sm_count();
   if (grid > p.n_items) grid = p.n_items;
   kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tb, tmk, p, status);
-  TPF_CUDA_OK(cudaGetLastError());
+  TPF_LAUNCH_OK();
   return TPF_OK;
 }
 

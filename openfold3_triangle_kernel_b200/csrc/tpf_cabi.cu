@@ -27,7 +27,7 @@ int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out
                   const int64_t* k_strides, const int64_t* v_strides, const void* out, const float* lse,
                   const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
                   void* dq, void* dk, void* dv, float* delta, void* workspace, int64_t workspace_bytes, int64_t B,
-                  int64_t O, int64_t H, int64_t N, int64_t D, float scale, cudaStream_t stream);
+                  int64_t O, int64_t H, int64_t N, int64_t D, float scale, int stages, cudaStream_t stream);
 int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
                    const int64_t* k_strides, const int64_t* v_strides, const float* lse, const float* delta,
                    const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
@@ -57,6 +57,8 @@ extern "C" {
 const char* tpf_version(void) { return "tpf_b200 0.1 sm_100a"; }
 
 const char* tpf_last_error_string(void) { return tpf::last_error_buffer(); }
+
+int64_t tpf_launch_count(void) { return tpf::launch_counter().load(); }
 
 int tpf_device_status(int* status) {
   TPF_REQUIRE(status != nullptr, TPF_ERR_INVALID_ARGUMENT, "tpf_device_status: status is NULL");
@@ -104,6 +106,19 @@ int tpf_attn_bwd(const void* q, const void* k, const void* v, const void* d_out,
                  const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch, int64_t bias_batch,
                  void* dq, void* dk, void* dv, float* dbias, float* delta, void* workspace, int64_t workspace_bytes,
                  int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, void* stream) {
+  return tpf_attn_bwd_stages(q, k, v, d_out, q_strides, k_strides, v_strides, out, lse, mask, mask_pitch, bias,
+                             bias_pitch, bias_batch, dq, dk, dv, dbias, delta, workspace, workspace_bytes, B, O, H, N,
+                             D, scale, TPF_ATTN_BWD_STAGE_ALL, stream);
+}
+
+int tpf_attn_bwd_stages(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
+                        const int64_t* k_strides, const int64_t* v_strides, const void* out, const float* lse,
+                        const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch,
+                        int64_t bias_batch, void* dq, void* dk, void* dv, float* dbias, float* delta, void* workspace,
+                        int64_t workspace_bytes, int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale,
+                        int stages, void* stream) {
+  TPF_REQUIRE(stages > 0 && stages <= TPF_ATTN_BWD_STAGE_ALL, TPF_ERR_INVALID_ARGUMENT,
+              "tpf_attn_bwd_stages: stages must be a non-empty mask of TPF_ATTN_BWD_STAGE_*");
   TPF_REQUIRE(q_strides && k_strides && v_strides, TPF_ERR_INVALID_ARGUMENT, "tpf_attn_bwd: stride arrays are NULL");
   TPF_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, TPF_ERR_INVALID_ARGUMENT,
               "tpf_attn_bwd: workspace must be 256-byte aligned");
@@ -115,9 +130,13 @@ int tpf_attn_bwd(const void* q, const void* k, const void* v, const void* d_out,
               "tpf_attn_bwd: workspace of %lld bytes required, %lld given", (long long)(ws_a + ws_b),
               (long long)workspace_bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = tpf::attn_bwd_dqkv(q, k, v, d_out, q_strides, k_strides, v_strides, out, lse, mask, mask_pitch, bias,
-                              bias_pitch, bias_batch, dq, dk, dv, delta, workspace, ws_a, B, O, H, N, D, scale, st);
+  int rc = TPF_OK;
+  if (stages & (TPF_ATTN_BWD_STAGE_DELTA | TPF_ATTN_BWD_STAGE_DQKV))
+    rc = tpf::attn_bwd_dqkv(q, k, v, d_out, q_strides, k_strides, v_strides, out, lse, mask, mask_pitch, bias,
+                            bias_pitch, bias_batch, dq, dk, dv, delta, workspace, ws_a, B, O, H, N, D, scale,
+                            stages & 3, st);
   if (rc) return rc;
+  if (!(stages & TPF_ATTN_BWD_STAGE_DBIAS)) return TPF_OK;
   return tpf::attn_bwd_dbias(q, k, v, d_out, q_strides, k_strides, v_strides, lse, delta, mask, mask_pitch, bias,
                              bias_pitch, bias_batch, dbias, static_cast<char*>(workspace) + ws_a, ws_b, B, O, H, N, D,
                              scale, st);

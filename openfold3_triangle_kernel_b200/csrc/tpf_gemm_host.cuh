@@ -45,7 +45,7 @@ int launch_gemm(const void* A, int64_t lda, int64_t bsa, const void* B, int64_t 
   if (grid > tiles) grid = tiles;
   if (grid < 1) return TPF_OK;
   kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, sh, ep, status);
-  TPF_CUDA_OK(cudaGetLastError());
+  TPF_LAUNCH_OK();
   return TPF_OK;
 }
 

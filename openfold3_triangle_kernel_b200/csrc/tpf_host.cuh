@@ -10,6 +10,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "../../include/tpf_b200.h"  // TPF_OK / TPF_ERR_* codes
 
 namespace tpf {
@@ -36,6 +38,19 @@ inline int fail(int code, const char* fmt, ...) {
     if (_e != cudaSuccess)                                                                            \
       return ::tpf::fail(TPF_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
                          __FILE__, __LINE__);                                                         \
+  } while (0)
+
+// Number of kernel launches this process has issued through the library (all host threads).
+inline std::atomic<long long>& launch_counter() {
+  static std::atomic<long long> n{0};
+  return n;
+}
+
+// After every <<<...>>>: count the launch and surface a launch error.
+#define TPF_LAUNCH_OK()                          \
+  do {                                           \
+    ::tpf::launch_counter().fetch_add(1);        \
+    TPF_CUDA_OK(cudaGetLastError());             \
   } while (0)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

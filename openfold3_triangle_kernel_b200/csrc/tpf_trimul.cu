@@ -482,7 +482,7 @@ static int pack_weights(const float* p_in, const float* g_in, const float* p_out
   pk->Wz = base + 10 * C * C;
   pk->WzT = base + 11 * C * C;
   trimul_pack_weights_kernel<<<64, 256, 0, stream>>>(p_in, g_in, p_out, g_out, pk->W5, pk->W5T, pk->Wz, pk->WzT, C);
-  TPF_CUDA_OK(cudaGetLastError());
+  TPF_LAUNCH_OK();
   return TPF_OK;
 }
 
@@ -505,7 +505,7 @@ static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk
     const int64_t warps = (R + L::RPW - 1) / L::RPW;
     const int64_t blocks = (warps + 7) / 8;
     trimul_ln_fwd_kernel<C><<<(unsigned)blocks, 256, 0, stream>>>(z, gin, bin, zln, mean_in, rstd_in, R);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
   int rc;
   {
@@ -519,7 +519,7 @@ static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk
     const int tiles = (int)((NN + 63) / 64);
     trimul_xnorm_fwd_kernel<C><<<(unsigned)(B * tiles), 256, 0, stream>>>(x_cm, gout, bout, xln, mean_out, rstd_out,
                                                                           NN, tiles);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
   {
     using Cfg = GemmCfg<128, C, 128, false, 128, false, 4>;
@@ -596,7 +596,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     int blocks = (int)((R * C / 8 + 255) / 256);
     if (blocks > 16 * sm_count()) blocks = 16 * sm_count();
     trimul_out_gate_bwd_kernel<<<blocks, 256, 0, stream>>>(d_out, out, gate, w.d_y, w.d_proj5, R, C);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
   // 2. d_xln = d_y Wz ; d_wz = d_y^T xln
   {
@@ -613,7 +613,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     WgradDst d;
     for (int i = 0; i < 5; ++i) d.dst[i] = d_p_out;
     trimul_wgrad_fold_kernel<<<(C * C + 255) / 256, 256, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
   // 3. output norm backward -> d_x (channel-major), d_gamma_out, d_beta_out
   {
@@ -627,10 +627,10 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     }
     kern<<<(unsigned)(B * tiles), 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out,
                                                        NN, tiles);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
     trimul_colsum_fold_kernel<<<(2 * C + 255) / 256, 256, 0, stream>>>(w.part_ln_out, w.blocks_ln_out, 2 * C, d_gout,
                                                                        d_bout, C);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
   // 4. contraction backward
   if (!incoming) {
@@ -667,16 +667,16 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     d.dst[3] = d_g_in + C * C;      // b_g
     d.dst[4] = d_g_out;             // g
     trimul_wgrad_fold_kernel<<<(5 * C * C + 255) / 256, 256, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
   // 7. input norm backward
   {
     trimul_ln_bwd_kernel<C><<<w.blocks_ln_in, 256, 0, stream>>>(d_zln, z, gin, mean_in, rstd_in, d_z, w.part_ln_in, R,
                                                                 w.rows_per_block_in);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
     trimul_colsum_fold_kernel<<<(2 * C + 255) / 256, 256, 0, stream>>>(w.part_ln_in, w.blocks_ln_in, 2 * C, d_gin,
                                                                        d_bin, C);
-    TPF_CUDA_OK(cudaGetLastError());
+    TPF_LAUNCH_OK();
   }
   return TPF_OK;
 }
