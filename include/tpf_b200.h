@@ -114,6 +114,30 @@ int tpf_attn_bwd(const void* q, const void* k, const void* v, const void* d_out,
                  void* workspace, int64_t workspace_bytes,
                  int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, void* stream);
 
+/* Capacity in bytes of the scratch array built into the library (see tpf_attn_bwd_static_scratch). */
+int64_t tpf_attn_bwd_static_scratch_capacity(void);
+
+/* tpf_attn_bwd for callers that cannot allocate device memory (code between stream-capture
+ * begin/end, plugin or real-time hosts that get their memory once at start-up, runtimes that
+ * own the device heap): same inputs, outputs and results as tpf_attn_bwd, but the scratch is a
+ * fixed 16 MiB array inside the library image instead of a caller workspace.  The call allocates
+ * and frees nothing.  This entry point has no counterpart in the reference.
+ *  - Shapes whose scratch need (tpf_attn_bwd_workspace_bytes) exceeds the capacity are rejected
+ *    with TPF_ERR_WORKSPACE and a message; nothing is launched.
+ *  - The first call on each device looks up the array's device address (a synchronous runtime
+ *    query); make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps whatever the last call left there.
+ *    Nothing in it needs clearing between calls, but two calls that overlap on the GPU
+ *    (different streams, no ordering) race on it; order them.
+ *  - Every GPU that loads the library keeps the 16 MiB until the process exits. */
+int tpf_attn_bwd_static_scratch(const void* q, const void* k, const void* v, const void* d_out,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const void* out, const float* lse,
+                 const float* mask, int64_t mask_pitch,
+                 const void* bias, int64_t bias_pitch, int64_t bias_batch,
+                 void* dq, void* dk, void* dv, float* dbias, float* delta,
+                 int64_t B, int64_t O, int64_t H, int64_t N, int64_t D, float scale, void* stream);
+
 /* Scratch sizes of the TriMul entry points (bytes; 256-byte aligned buffers). */
 int64_t tpf_trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
 int64_t tpf_trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C);

@@ -29,6 +29,9 @@ SIGNATURES = {
     "tpf_launch_count": [],
     "tpf_attn_bwd_stages": [_P, _P, _P, _P, _PI, _PI, _PI, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I,
                             _I, _I, _I, _I, _I, _f, _i, _P],
+    "tpf_attn_bwd_static_scratch_capacity": [],
+    "tpf_attn_bwd_static_scratch": [_P, _P, _P, _P, _PI, _PI, _PI, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P,
+                                    _I, _I, _I, _I, _I, _f, _P],
     "tpf_attn_bwd": [_P, _P, _P, _P, _PI, _PI, _PI, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I,
                      _I, _I, _I, _I, _I, _f, _P],
     "tpf_trimul_fwd_workspace_bytes": [_I, _I, _I],

@@ -1076,4 +1076,67 @@ int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_ou
   return TPF_OK;
 }
 
+// =============================================================================================
+// Backward with library-owned scratch: for callers that cannot allocate device memory themselves
+// =============================================================================================
+// Some hosts of this library may not call cudaMalloc (or any allocating routine) around the
+// backward pass: code running between graph-capture begin/end, real-time or plugin hosts whose
+// memory is handed out once at start-up, and foreign runtimes that own the device heap.  For them
+// the scratch of the backward pass (per-CTA dQ running sums, dBias chunk planes) lives in a fixed
+// array that is part of the library image.  Every GPU that loads the library holds these
+// kStaticScratchBytes until the process exits.
+constexpr int64_t kStaticScratchBytes = 16ll << 20;  // 16 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int64_t attn_bwd_static_scratch_capacity() { return kStaticScratchBytes; }
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
+// address is looked up once per device (with that device current) and cached.
+static int static_scratch_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* addr[kMaxDevices] = {};
+  static std::atomic<bool> ready[kMaxDevices] = {};
+  int dev = 0;
+  TPF_CUDA_OK(cudaGetDevice(&dev));
+  TPF_REQUIRE(dev >= 0 && dev < kMaxDevices, TPF_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    void* p = nullptr;
+    TPF_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    TPF_REQUIRE(p != nullptr && (reinterpret_cast<uintptr_t>(p) & 255) == 0, TPF_ERR_CUDA,
+                "static scratch address lookup returned a bad pointer");
+    addr[dev] = p;
+    ready[dev].store(true, std::memory_order_release);
+  }
+  *out = addr[dev];
+  return TPF_OK;
+}
+
+int attn_bwd_static_scratch(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
+                            const int64_t* k_strides, const int64_t* v_strides, const void* out, const float* lse,
+                            const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch,
+                            int64_t bias_batch, void* dq, void* dk, void* dv, float* dbias, float* delta, int64_t B,
+                            int64_t O, int64_t H, int64_t N, int64_t D, float scale, cudaStream_t stream) {
+  TPF_REQUIRE(B > 0 && O > 0 && H > 0 && N > 0 && (bias_batch == 1 || bias_batch == B), TPF_ERR_INVALID_ARGUMENT,
+              "attn_bwd (library scratch): bad extents");
+  TPF_REQUIRE(D == 16 || D == 32 || D == 64, TPF_ERR_UNSUPPORTED,
+              "attn_bwd (library scratch): head dim %lld not in {16,32,64}", (long long)D);
+  const int64_t ws_a = (attn_bwd_workspace_bytes(B, O, H, N, D) + 255) / 256 * 256;
+  const int64_t ws_b = (attn_dbias_workspace_bytes(B, O, H, N, bias_batch) + 255) / 256 * 256;
+  TPF_REQUIRE(ws_a + ws_b <= kStaticScratchBytes, TPF_ERR_WORKSPACE,
+              "attn_bwd (library scratch): this shape needs %lld bytes of scratch, the built-in array holds %lld; "
+              "use tpf_attn_bwd with a caller-provided workspace",
+              (long long)(ws_a + ws_b), (long long)kStaticScratchBytes);
+  void* base = nullptr;
+  int rc = static_scratch_address(&base);
+  if (rc) return rc;
+  // Nothing in the scratch has to start at zero: the dQ running sums are written by the first key
+  // strip before they are read, and every dBias chunk plane is fully overwritten.
+  rc = attn_bwd_dqkv(q, k, v, d_out, q_strides, k_strides, v_strides, out, lse, mask, mask_pitch, bias, bias_pitch,
+                     bias_batch, dq, dk, dv, delta, base, ws_a, B, O, H, N, D, scale, 3, stream);
+  if (rc) return rc;
+  return attn_bwd_dbias(q, k, v, d_out, q_strides, k_strides, v_strides, lse, delta, mask, mask_pitch, bias,
+                        bias_pitch, bias_batch, dbias, static_cast<char*>(base) + ws_a, ws_b, B, O, H, N, D, scale,
+                        stream);
+}
+
 }  // namespace tpf

@@ -34,6 +34,12 @@ int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_ou
                    float* dbias, void* workspace, int64_t workspace_bytes, int64_t B, int64_t O, int64_t H, int64_t N,
                    int64_t D, float scale, cudaStream_t stream);
 
+int64_t attn_bwd_static_scratch_capacity();
+int attn_bwd_static_scratch(const void* q, const void* k, const void* v, const void* d_out, const int64_t* q_strides,
+                            const int64_t* k_strides, const int64_t* v_strides, const void* out, const float* lse,
+                            const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch,
+                            int64_t bias_batch, void* dq, void* dk, void* dv, float* dbias, float* delta, int64_t B,
+                            int64_t O, int64_t H, int64_t N, int64_t D, float scale, cudaStream_t stream);
 int trimul_status_fetch_and_clear(int* out);
 int64_t trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
 int64_t trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
@@ -140,6 +146,21 @@ int tpf_attn_bwd_stages(const void* q, const void* k, const void* v, const void*
   return tpf::attn_bwd_dbias(q, k, v, d_out, q_strides, k_strides, v_strides, lse, delta, mask, mask_pitch, bias,
                              bias_pitch, bias_batch, dbias, static_cast<char*>(workspace) + ws_a, ws_b, B, O, H, N, D,
                              scale, st);
+}
+
+int64_t tpf_attn_bwd_static_scratch_capacity(void) { return tpf::attn_bwd_static_scratch_capacity(); }
+
+int tpf_attn_bwd_static_scratch(const void* q, const void* k, const void* v, const void* d_out,
+                                const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                const void* out, const float* lse, const float* mask, int64_t mask_pitch,
+                                const void* bias, int64_t bias_pitch, int64_t bias_batch, void* dq, void* dk, void* dv,
+                                float* dbias, float* delta, int64_t B, int64_t O, int64_t H, int64_t N, int64_t D,
+                                float scale, void* stream) {
+  TPF_REQUIRE(q_strides && k_strides && v_strides, TPF_ERR_INVALID_ARGUMENT,
+              "tpf_attn_bwd_static_scratch: stride arrays are NULL");
+  return tpf::attn_bwd_static_scratch(q, k, v, d_out, q_strides, k_strides, v_strides, out, lse, mask, mask_pitch,
+                                      bias, bias_pitch, bias_batch, dq, dk, dv, dbias, delta, B, O, H, N, D, scale,
+                                      static_cast<cudaStream_t>(stream));
 }
 
 static bool trimul_shape_ok(int64_t B, int64_t N, int64_t C) {

@@ -1,0 +1,79 @@
+"""tpf_attn_bwd_static_scratch: the backward pass for hosts that cannot allocate device memory
+(code inside a stream capture, plugin hosts that receive their memory once, runtimes that own the
+device heap).  It must give exactly what tpf_attn_bwd gives with a caller workspace, on
+repeated calls that reuse the library's built-in scratch array, and must refuse shapes whose
+scratch would not fit.  Collected last so a failure here cannot hide other results."""
+import math
+
+import pytest
+import torch
+
+from openfold3_triangle_kernel_b200 import _cabi as C
+from oracle.inputs import attention_inputs
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a CUDA device")]
+
+
+def _buffers(B, O, H, N, D, seed):
+    dev = "cuda"
+    inp = attention_inputs(B, O, H, N, D, seed=seed, mask_mode="trailing15")
+    q, k, v = (inp[n].to(dev) for n in ("q", "k", "v"))
+    bias = inp["pair_bias"].to(dev).reshape(1, H, N, N).contiguous()
+    mask = inp["res_mask"].to(dev).reshape(B, O, N).contiguous()
+    out = torch.empty(B, O, N, H, D, device=dev, dtype=torch.bfloat16)
+    lse = torch.empty(B, O, H, N, device=dev)
+    qs = C.i64_array(q.stride()[:4])
+    scale = 1.0 / math.sqrt(D)
+    C.call("tpf_attn_fwd", C.ptr(q), C.ptr(k), C.ptr(v), qs, qs, qs, C.ptr(mask), N, C.ptr(bias), N, 1, C.ptr(out),
+           C.ptr(lse), B, O, H, N, D, scale, C.current_stream())
+    d_out = torch.randn(B, O, N, H, D, device=dev, generator=torch.Generator(device=dev).manual_seed(seed)).bfloat16()
+    return dict(q=q, k=k, v=v, bias=bias, mask=mask, out=out, lse=lse, d_out=d_out, qs=qs, scale=scale)
+
+
+def _grads(B, O, H, N, D):
+    dev = "cuda"
+    e = lambda: torch.full((B, O, H, N, D), float("nan"), device=dev, dtype=torch.bfloat16)  # noqa: E731
+    return dict(dq=e(), dk=e(), dv=e(), dbias=torch.full((1, H, N, N), float("nan"), device=dev),
+                delta=torch.empty(B, O, H, N, device=dev))
+
+
+def _call(name, t, g, shape, extra=()):
+    B, O, H, N, D = shape
+    p = C.ptr
+    C.call(name, p(t["q"]), p(t["k"]), p(t["v"]), p(t["d_out"]), t["qs"], t["qs"], t["qs"], p(t["out"]), p(t["lse"]),
+           p(t["mask"]), N, p(t["bias"]), N, 1, p(g["dq"]), p(g["dk"]), p(g["dv"]), p(g["dbias"]), p(g["delta"]),
+           *extra, B, O, H, N, D, t["scale"], C.current_stream())
+
+
+@pytest.mark.parametrize("shape", [(1, 12, 4, 200, 32), (1, 6, 2, 512, 32)], ids=["one_strip", "two_strips"])
+def test_static_scratch_matches_workspace_entry_twice_in_a_row(shape):
+    B, O, H, N, D = shape
+    lib = C.load()
+    need = lib.tpf_attn_bwd_workspace_bytes(B, O, H, N, D, 1)
+    assert 0 < need <= lib.tpf_attn_bwd_static_scratch_capacity()      # the case really uses scratch
+    for seed in (3, 4):                                                # two calls in a row, different data
+        t = _buffers(B, O, H, N, D, seed)
+        ref, got = _grads(B, O, H, N, D), _grads(B, O, H, N, D)
+        ws = torch.empty(need, device="cuda", dtype=torch.uint8)
+        _call("tpf_attn_bwd", t, ref, shape, extra=(C.ptr(ws), need))
+        before = torch.cuda.memory_allocated()
+        _call("tpf_attn_bwd_static_scratch", t, got, shape)
+        assert torch.cuda.memory_allocated() == before
+        torch.cuda.synchronize()
+        assert C.device_status() == 0
+        for n in ("dq", "dk", "dv", "dbias", "delta"):
+            # same kernels, same summation order: identical bits
+            assert torch.equal(got[n].view(torch.uint8), ref[n].view(torch.uint8)), n
+            assert torch.isfinite(got[n].float()).all(), n
+
+
+def test_static_scratch_rejects_shapes_that_do_not_fit():
+    lib = C.load()
+    B, O, H, N, D = 1, 64, 4, 1536, 32
+    assert lib.tpf_attn_bwd_workspace_bytes(B, O, H, N, D, 1) > lib.tpf_attn_bwd_static_scratch_capacity()
+    one = torch.zeros(64, device="cuda")
+    p = C.ptr(one)
+    st = C.i64_array([1, 1, 1, 1])
+    with pytest.raises(C.TpfError, match="built-in array holds"):
+        C.call("tpf_attn_bwd_static_scratch", p, p, p, p, st, st, st, p, p, p, N, p, N, 1, p, p, p, p, p, B, O, H, N,
+               D, 0.1, C.current_stream())
