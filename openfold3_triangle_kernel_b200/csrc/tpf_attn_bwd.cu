@@ -467,14 +467,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool tail = (kt + 1) * 128 > p.N;
       float pf[64];
       uint32_t ppk[32];
+      {
+        uint32_t(*r32)[32] = reinterpret_cast<uint32_t(*)[32]>(pf);
+        tmem_ld32(t_s, r32[0]);
+        tmem_ld32(t_s + 32, r32[1]);
+        tmem_ld_wait();
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t raw[16];
-        tmem_ld16(t_s + 16 * c, raw);
+        const uint32_t* raw = reinterpret_cast<const uint32_t*>(pf) + 16 * c;
         uint4 bv[2];
 #pragma unroll
         for (int u = 0; u < 2; ++u) bv[u] = *reinterpret_cast<const uint4*>(bias_row + (((2 * c + u) ^ (row & 7)) << 4));
-        tmem_ld_wait();
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const uint32_t bw[4] = {bv[u].x, bv[u].y, bv[u].z, bv[u].w};
@@ -528,11 +532,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       dpfull_ph ^= 1;
       tc_fence_after();
       uint32_t dpk[32];
+      uint32_t rdp[64];
+      {
+        uint32_t(*r32)[32] = reinterpret_cast<uint32_t(*)[32]>(rdp);
+        tmem_ld32(t_dp, r32[0]);
+        tmem_ld32(t_dp + 32, r32[1]);
+        tmem_ld_wait();
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t raw[16];
-        tmem_ld16(t_dp + 16 * c, raw);
-        tmem_ld_wait();
+        const uint32_t* raw = rdp + 16 * c;
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
           const float d0 = pf[16 * c + i] * (__uint_as_float(raw[i]) - delta);
@@ -770,17 +779,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
     for (int i = 0; i < 64; ++i) acc[i] = 0.f;
 
-    // bias row (64 bf16) -> packed registers
-    mbar_wait(bias_full, 0, wctx);
-    uint32_t bpk[32];
-    {
-      const uint8_t* brow = smem + Cfg::OFF_BIAS + hf * 16384 + row * 128;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const uint4 v4 = *reinterpret_cast<const uint4*>(brow + ((u ^ (row & 7)) << 4));
-        bpk[4 * u] = v4.x; bpk[4 * u + 1] = v4.y; bpk[4 * u + 2] = v4.z; bpk[4 * u + 3] = v4.w;
-      }
-    }
+    mbar_wait(bias_full, 0, wctx);  // the bias tile of this CTA stays in shared memory
 
     auto load_row_scalars = [&](int pl, float& nl2, float& dl) {
       nl2 = -INFINITY;
@@ -808,40 +807,46 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_ST + s * Cfg::STAGE + 4 * Cfg::TILE) + 64 * hf;
       const uint32_t t_s = tmem_addr(tmem_base, lane_base, buf * 256 + 64 * hf);
       const uint32_t t_dp = tmem_addr(tmem_base, lane_base, buf * 256 + 128 + 64 * hf);
+      const uint8_t* brow = smem + Cfg::OFF_BIAS + hf * 16384 + row * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[16], rd[16];
-        tmem_ld16(t_s + 16 * c, rs);
-        tmem_ld16(t_dp + 16 * c, rd);
+      for (int hh = 0; hh < 2; ++hh) {  // 32 columns per half: two TMEM loads in flight, one wait
+        const int base = 32 * hh;
+        uint32_t rs[32], rd[32];
+        tmem_ld32(t_s + base, rs);
+        tmem_ld32(t_dp + base, rd);
         tmem_ld_wait();
+        if (hh == 1) {
+          // the whole TMEM tile is in registers: the next S / dP pair may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sdp_free[buf]);
+        }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const float4 mk0 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u);
-          const float4 mk1 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u + 4);
+        for (int u = 0; u < 4; ++u) {  // 8 columns per step
+          const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((4 * hh + u) ^ (row & 7)) << 4));
+          const uint32_t bw4[4] = {bv.x, bv.y, bv.z, bv.w};
+          const float4 mk0 = *reinterpret_cast<const float4*>(mask_row + base + 8 * u);
+          const float4 mk1 = *reinterpret_cast<const float4*>(mask_row + base + 8 * u + 4);
           const float mk[8] = {mk0.x, mk0.y, mk0.z, mk0.w, mk1.x, mk1.y, mk1.z, mk1.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i0 = 8 * u + 2 * e;
-            const uint32_t bw = bpk[8 * c + 4 * u + e];
+            const uint32_t bw = bw4[e];
             float v0 = fmaf(__uint_as_float(rs[i0]), scale, __uint_as_float(bw << 16)) + mk[2 * e];
             float v1 = fmaf(__uint_as_float(rs[i0 + 1]), scale, __uint_as_float(bw & 0xFFFF0000u)) + mk[2 * e + 1];
             if (tail) {
-              if (kt * 128 + 64 * hf + 16 * c + i0 >= p.N) v0 = -INFINITY;
-              if (kt * 128 + 64 * hf + 16 * c + i0 + 1 >= p.N) v1 = -INFINITY;
+              if (kt * 128 + 64 * hf + base + i0 >= p.N) v0 = -INFINITY;
+              if (kt * 128 + 64 * hf + base + i0 + 1 >= p.N) v1 = -INFINITY;
             }
             const float p0 = ex2_approx(fmaf(v0, kLog2e, neg_lse2));
             const float p1 = ex2_approx(fmaf(v1, kLog2e, neg_lse2));
-            acc[16 * c + i0] = fmaf(p0, __uint_as_float(rd[i0]) - delta, acc[16 * c + i0]);
-            acc[16 * c + i0 + 1] = fmaf(p1, __uint_as_float(rd[i0 + 1]) - delta, acc[16 * c + i0 + 1]);
+            acc[base + i0] = fmaf(p0, __uint_as_float(rd[i0]) - delta, acc[base + i0]);
+            acc[base + i0 + 1] = fmaf(p1, __uint_as_float(rd[i0 + 1]) - delta, acc[base + i0 + 1]);
           }
         }
       }
-      tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&sdp_free[buf]);
-        mbar_arrive(&empty[s]);
-      }
+      if (lane == 0) mbar_arrive(&empty[s]);
       buf ^= 1;
       if (++s == NST) {
         s = 0;

@@ -324,18 +324,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint8_t* bias_tile = smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE;
         const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_MASK + (w * NKV + v_s) * 512);
         const bool tail = (j + 1) * 128 > p.N;
-        float tmax = -INFINITY;
+        // all 128 logits of the row: four TMEM loads in flight, one wait
+        {
+          uint32_t(*raw)[32] = reinterpret_cast<uint32_t(*)[32]>(s);
+          tmem_ld32(t_s + 0, raw[0]);
+          tmem_ld32(t_s + 32, raw[1]);
+          tmem_ld32(t_s + 64, raw[2]);
+          tmem_ld32(t_s + 96, raw[3]);
+          tmem_ld_wait();
+        }
+        float tmax4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {  // 16 key columns per step
-          uint32_t raw[16];
-          tmem_ld16(t_s + 16 * c, raw);
           // bias: 16 bf16 of this row = 2 x 16 B in the 128-byte-swizzled half tile
           const uint8_t* brow = bias_tile + (c >> 2) * 16384 + row * 128;
           uint4 bv[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u)
             bv[u] = *reinterpret_cast<const uint4*>(brow + ((((c & 3) * 2 + u) ^ (row & 7)) << 4));
-          tmem_ld_wait();
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             const uint32_t bw[4] = {bv[u].x, bv[u].y, bv[u].z, bv[u].w};
@@ -346,19 +352,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int e = 0; e < 4; ++e) {
               const float b_lo = __uint_as_float(bw[e] << 16);
               const float b_hi = __uint_as_float(bw[e] & 0xFFFF0000u);
-              const int i0 = 8 * u + 2 * e;
-              float v0 = fmaf(__uint_as_float(raw[i0]), scale, b_lo) + mk[2 * e];
-              float v1 = fmaf(__uint_as_float(raw[i0 + 1]), scale, b_hi) + mk[2 * e + 1];
+              const int i0 = 16 * c + 8 * u + 2 * e;
+              float v0 = fmaf(s[i0], scale, b_lo) + mk[2 * e];
+              float v1 = fmaf(s[i0 + 1], scale, b_hi) + mk[2 * e + 1];
               if (tail) {
-                if (j * 128 + 16 * c + i0 >= p.N) v0 = -INFINITY;
-                if (j * 128 + 16 * c + i0 + 1 >= p.N) v1 = -INFINITY;
+                if (j * 128 + i0 >= p.N) v0 = -INFINITY;
+                if (j * 128 + i0 + 1 >= p.N) v1 = -INFINITY;
               }
-              s[16 * c + i0] = v0;
-              s[16 * c + i0 + 1] = v1;
-              tmax = fmaxf(tmax, fmaxf(v0, v1));
+              s[i0] = v0;
+              s[i0 + 1] = v1;
+              tmax4[e] = fmaxf(tmax4[e], fmaxf(v0, v1));
             }
           }
         }
+        const float tmax = fmaxf(fmaxf(tmax4[0], tmax4[1]), fmaxf(tmax4[2], tmax4[3]));
         // S, the bias tile and the mask row now live in registers
         tc_fence_before();
         __syncwarp();
@@ -401,7 +408,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         const float neg_m2 = (m_ref == -INFINITY) ? 0.f : -m_ref * kLog2e;
 
-        float rsum = 0.f;
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint8_t* prow = p_tile + (c >> 1) * 16384 + row * 128;
@@ -411,7 +418,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               e[i] = ex2_approx(fmaf(s[32 * c + 8 * u + i], kLog2e, neg_m2));
-              rsum += e[i];
+              rs4[i & 3] += e[i];
             }
             uint4 pk;
             pk.x = pack_bf16x2(e[0], e[1]);
@@ -421,7 +428,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             *reinterpret_cast<uint4*>(prow + ((((c & 1) * 4 + u) ^ (row & 7)) << 4)) = pk;
           }
         }
-        l_run += rsum;
+        l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
         fence_async_smem();
         tc_fence_before();
         __syncwarp();

@@ -55,8 +55,9 @@ struct EpiStore {
     int64_t batch_stride;
   };
   static constexpr bool kPaired = false;
+  static constexpr int kSmemPerWarp = 0;  // bytes of per-warp epilogue scratch
   __device__ static __forceinline__ void apply(const Params& p, const GemmShape& sh, int b, int m, int n0,
-                                               const float (&v)[32]) {
+                                               const float (&v)[32], float*, int) {
     if (m >= sh.M) return;
     OutT* row = p.D + (int64_t)b * p.batch_stride + (int64_t)m * p.ldd + n0;
     if (n0 + 32 <= sh.N && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
@@ -98,6 +99,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx wctx{abort_flag, status};
+  // per-warp epilogue scratch (only when the epilogue asks for it) sits behind the 256-byte barrier block
+  uint8_t* epi_smem = smem + Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES) + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -212,6 +215,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     const int lane_base = 32 * (warp & 3);
+    float* wsm = reinterpret_cast<float*>(epi_smem + (warp - 2) * Epi::kSmemPerWarp);
     int acc = 0;
     uint32_t acc_ph = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
@@ -232,7 +236,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-          if (n0 + c < sh.N) Epi::apply(ep, sh, b, m, n0 + c, v);
+          if (n0 + c < sh.N) Epi::apply(ep, sh, b, m, n0 + c, v, wsm, lane);
         }
       } else {
         // Column c (first half of the tile) pairs with column c + BN/2.
@@ -248,7 +252,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             v0[i] = __uint_as_float(raw0[i]);
             v1[i] = __uint_as_float(raw1[i]);
           }
-          Epi::apply2(ep, sh, b, m, n0, c, v0, v1);
+          Epi::apply2(ep, sh, b, m, n0, c, v0, v1, wsm, lane);
         }
       }
       tc_fence_before();

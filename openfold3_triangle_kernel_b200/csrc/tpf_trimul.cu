@@ -130,19 +130,27 @@ __global__ void __launch_bounds__(256) trimul_xnorm_fwd_kernel(const bf16* __res
   __shared__ float tile[C][65];
   const int bb = blockIdx.x / tiles_per_batch;
   const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * 64;
-  for (int idx = threadIdx.x; idx < C * 64; idx += 256) {
-    const int c = idx >> 6, j = idx & 63;
-    tile[c][j] = (r0 + j < NN) ? __bfloat162float(x_cm[((int64_t)bb * C + c) * NN + r0 + j]) : 0.f;
+  // 16-byte loads: 8 consecutive rows of one channel (NN is a multiple of 8)
+  for (int idx = threadIdx.x; idx < C * 8; idx += 256) {
+    const int c = idx >> 3, j8 = idx & 7;
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    if (r0 + 8 * j8 < NN) u = *reinterpret_cast<const uint4*>(x_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      tile[c][8 * j8 + 2 * e] = bf16_lo(w[e]);
+      tile[c][8 * j8 + 2 * e + 1] = bf16_hi(w[e]);
+    }
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int j = warp; j < 64; j += 8) {
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int c = lane; c < C; c += 32) {
-      const float v = tile[c][j];
-      s1 += v;
-      s2 += v * v;
+    for (int c = 2 * lane; c < C; c += 64) {
+      const float v0 = tile[c][j], v1 = tile[c + 1][j];
+      s1 += v0 + v1;
+      s2 += v0 * v0 + v1 * v1;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -154,8 +162,12 @@ __global__ void __launch_bounds__(256) trimul_xnorm_fwd_kernel(const bf16* __res
     if (r0 + j < NN) {
       const int64_t row = (int64_t)bb * NN + r0 + j;
 #pragma unroll
-      for (int c = lane; c < C; c += 32)
-        xln[row * C + c] = __float2bfloat16((tile[c][j] - mu) * rs * gamma[c] + beta[c]);
+      for (int c = 2 * lane; c < C; c += 64) {
+        const float2 g = *reinterpret_cast<const float2*>(gamma + c);
+        const float2 b = *reinterpret_cast<const float2*>(beta + c);
+        *reinterpret_cast<uint32_t*>(xln + row * C + c) =
+            pack_bf16x2((tile[c][j] - mu) * rs * g.x + b.x, (tile[c + 1][j] - mu) * rs * g.y + b.y);
+      }
       if (lane == 0) {
         mean[row] = mu;
         rstd[row] = rs;
@@ -168,6 +180,9 @@ __global__ void __launch_bounds__(256) trimul_xnorm_fwd_kernel(const bf16* __res
 // GEMM epilogues
 // =============================================================================================
 // Projection + gating.  GEMM N axis = [a_p | a_g] [b_p | b_g] [g | pad], one tile of width 2C each.
+// a and b are stored channel-major.  Each lane owns one row of the accumulator tile, which would
+// make 2-byte scattered stores; the 32x32 block is transposed through a per-warp smem tile so
+// that each lane writes 32 consecutive rows of ONE channel (4 x 16 bytes).
 struct EpiProjGate {
   struct Params {
     bf16* a_cm;        // [B*C][NN]
@@ -178,11 +193,12 @@ struct EpiProjGate {
     int64_t NN;
   };
   static constexpr bool kPaired = true;
+  static constexpr int kSmemPerWarp = 32 * 33 * 4;
   __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
-                                                const float (&v0)[32], const float (&v1)[32]) {
-    if (m >= sh.M) return;
+                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane) {
     const int which = n0 / (2 * p.C);
     if (which == 2) {
+      if (m >= sh.M) return;
       bf16* row = p.gate + (int64_t)m * p.C + c0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -195,11 +211,23 @@ struct EpiProjGate {
       }
       return;
     }
-    const float mk = p.mask[m];
-    const int64_t bb = m / p.NN, rr = m - bb * p.NN;
-    bf16* dst = (which == 0 ? p.a_cm : p.b_cm) + (bb * p.C + c0) * p.NN + rr;
+    const float mk = (m < sh.M) ? p.mask[m] : 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) dst[(int64_t)i * p.NN] = __float2bfloat16(v0[i] * sigmoid_fast(v1[i]) * mk);
+    for (int i = 0; i < 32; ++i) wsm[lane * 33 + i] = v0[i] * sigmoid_fast(v1[i]) * mk;
+    __syncwarp();
+    const int m_base = m - lane;  // first row of this warp's 32-row block (a multiple of 32)
+    const int64_t bb = m_base / p.NN, rr = m_base - bb * p.NN;
+    bf16* dst = (which == 0 ? p.a_cm : p.b_cm) + (bb * p.C + c0 + lane) * p.NN + rr;  // lane = channel
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint4 u;
+      u.x = pack_bf16x2(wsm[(8 * g + 0) * 33 + lane], wsm[(8 * g + 1) * 33 + lane]);
+      u.y = pack_bf16x2(wsm[(8 * g + 2) * 33 + lane], wsm[(8 * g + 3) * 33 + lane]);
+      u.z = pack_bf16x2(wsm[(8 * g + 4) * 33 + lane], wsm[(8 * g + 5) * 33 + lane]);
+      u.w = pack_bf16x2(wsm[(8 * g + 6) * 33 + lane], wsm[(8 * g + 7) * 33 + lane]);
+      if (m_base + 8 * g + 7 < sh.M) *reinterpret_cast<uint4*>(dst + 8 * g) = u;
+    }
+    __syncwarp();
   }
 };
 
@@ -211,8 +239,9 @@ struct EpiOutGate {
     int C;
   };
   static constexpr bool kPaired = false;
+  static constexpr int kSmemPerWarp = 0;
   __device__ static __forceinline__ void apply(const Params& p, const GemmShape& sh, int, int m, int n0,
-                                               const float (&v)[32]) {
+                                               const float (&v)[32], float*, int) {
     if (m >= sh.M) return;
     const bf16* g = p.gate + (int64_t)m * p.C + n0;
     bf16* o = p.out + (int64_t)m * p.C + n0;
@@ -241,23 +270,40 @@ struct EpiGateSplitBwd {
     int64_t NN;
   };
   static constexpr bool kPaired = true;
+  static constexpr int kSmemPerWarp = 32 * 33 * 4;
   __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
-                                                const float (&v0)[32], const float (&v1)[32]) {
-    if (m >= sh.M) return;
+                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane) {
     const int which = n0 / (2 * p.C);  // 0: a, 1: b
-    const float mk = p.mask[m];
-    const int64_t bb = m / p.NN, rr = m - bb * p.NN;
-    const bf16* src = (which == 0 ? p.da_cm : p.db_cm) + (bb * p.C + c0) * p.NN + rr;
-    bf16* dp = p.d_proj5 + (int64_t)m * 5 * p.C + which * 2 * p.C + c0;  // d_p block
-    bf16* dg = dp + p.C;                                                // d_g block
+    // incoming gradient block, channel-major: lane = channel reads 32 consecutive rows (4 x 16 bytes),
+    // transposed through smem so that afterwards lane = row holds its 32 channels
+    const int m_base = m - lane;
+    const int64_t bb = m_base / p.NN, rr = m_base - bb * p.NN;
+    const bf16* src = (which == 0 ? p.da_cm : p.db_cm) + (bb * p.C + c0 + lane) * p.NN + rr;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint4 u = make_uint4(0u, 0u, 0u, 0u);
+      if (m_base + 8 * g + 7 < sh.M) u = *reinterpret_cast<const uint4*>(src + 8 * g);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        wsm[(8 * g + 2 * e) * 33 + lane] = bf16_lo(w[e]);
+        wsm[(8 * g + 2 * e + 1) * 33 + lane] = bf16_hi(w[e]);
+      }
+    }
+    __syncwarp();
+    const float mk = (m < sh.M) ? p.mask[m] : 0.f;
     float o0[32], o1[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      const float d = __bfloat162float(src[(int64_t)i * p.NN]) * mk;
+      const float d = wsm[lane * 33 + i] * mk;
       const float s = sigmoid_fast(v1[i]);
       o0[i] = d * s;
       o1[i] = d * v0[i] * s * (1.f - s);
     }
+    __syncwarp();
+    if (m >= sh.M) return;
+    bf16* dp = p.d_proj5 + (int64_t)m * 5 * p.C + which * 2 * p.C + c0;  // d_p block
+    bf16* dg = dp + p.C;                                                // d_g block
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       uint4 u, w;
@@ -314,21 +360,40 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
   extern __shared__ float sm[];
   float(*xh)[65] = reinterpret_cast<float(*)[65]>(sm);            // xhat [C][65]
   float(*dg)[65] = reinterpret_cast<float(*)[65]>(sm + C * 65);   // d_xln [C][65]
-  __shared__ float s_m1[64], s_m2[64], s_rs[64];
+  __shared__ float s_m1[64], s_m2[64], s_rs[64], s_mu[64];
   const int bb = blockIdx.x / tiles_per_batch;
   const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * 64;
-  for (int idx = threadIdx.x; idx < C * 64; idx += 256) {
-    const int c = idx >> 6, j = idx & 63;
-    float v = 0.f;
-    if (r0 + j < NN) {
-      const int64_t row = (int64_t)bb * NN + r0 + j;
-      v = (__bfloat162float(x_cm[((int64_t)bb * C + c) * NN + r0 + j]) - mean[row]) * rstd[row];
-    }
-    xh[c][j] = v;
+  if (threadIdx.x < 64) {
+    const bool ok = r0 + threadIdx.x < NN;
+    s_mu[threadIdx.x] = ok ? mean[(int64_t)bb * NN + r0 + threadIdx.x] : 0.f;
+    s_rs[threadIdx.x] = ok ? rstd[(int64_t)bb * NN + r0 + threadIdx.x] : 0.f;
   }
-  for (int idx = threadIdx.x; idx < C * 64; idx += 256) {
-    const int j = idx / C, c = idx % C;
-    dg[c][j] = (r0 + j < NN) ? __bfloat162float(d_xln[((int64_t)bb * NN + r0 + j) * C + c]) : 0.f;
+  __syncthreads();
+  // x (channel-major): 8 consecutive rows of one channel per 16-byte load
+  for (int idx = threadIdx.x; idx < C * 8; idx += 256) {
+    const int c = idx >> 3, j8 = idx & 7;
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    const bool ok = r0 + 8 * j8 < NN;
+    if (ok) u = *reinterpret_cast<const uint4*>(x_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = 8 * j8 + 2 * e;
+      xh[c][j] = ok ? (bf16_lo(w[e]) - s_mu[j]) * s_rs[j] : 0.f;
+      xh[c][j + 1] = ok ? (bf16_hi(w[e]) - s_mu[j + 1]) * s_rs[j + 1] : 0.f;
+    }
+  }
+  // d_xln (row-major): 8 consecutive channels of one row per 16-byte load
+  for (int idx = threadIdx.x; idx < 64 * (C / 8); idx += 256) {
+    const int j = idx / (C / 8), c8 = idx % (C / 8);
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    if (r0 + j < NN) u = *reinterpret_cast<const uint4*>(d_xln + ((int64_t)bb * NN + r0 + j) * C + 8 * c8);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      dg[8 * c8 + 2 * e][j] = bf16_lo(w[e]);
+      dg[8 * c8 + 2 * e + 1][j] = bf16_hi(w[e]);
+    }
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -348,15 +413,23 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
     if (lane == 0) {
       s_m1[j] = a1 * (1.f / C);
       s_m2[j] = a2 * (1.f / C);
-      s_rs[j] = (r0 + j < NN) ? rstd[(int64_t)bb * NN + r0 + j] : 0.f;
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < C * 64; idx += 256) {
-    const int c = idx >> 6, j = idx & 63;
-    if (r0 + j < NN)
-      dx_cm[((int64_t)bb * C + c) * NN + r0 + j] =
-          __float2bfloat16(s_rs[j] * (gamma[c] * dg[c][j] - s_m1[j] - xh[c][j] * s_m2[j]));
+  for (int idx = threadIdx.x; idx < C * 8; idx += 256) {
+    const int c = idx >> 3, j8 = idx & 7;
+    if (r0 + 8 * j8 >= NN) continue;
+    const float gc = gamma[c];
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int j = 8 * j8 + e;
+      v[e] = s_rs[j] * (gc * dg[c][j] - s_m1[j] - xh[c][j] * s_m2[j]);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+    o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(dx_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8) = o;
   }
   if (threadIdx.x < C) {
     const int c = threadIdx.x;
@@ -439,16 +512,26 @@ __global__ void __launch_bounds__(256) trimul_ln_bwd_kernel(const bf16* __restri
   }
 }
 
-// out[j] = sum over blocks (ascending) of partials[blk][j], j < width
+// out[j] = fixed-order sum over blocks of partials[blk][j], j < width.  One CTA per 32 columns;
+// warp w adds blocks w, w+8, ... in ascending order, then the 8 warp sums are added in warp order.
 __global__ void __launch_bounds__(256) trimul_colsum_fold_kernel(const float* __restrict__ partials, int n_blocks,
                                                                  int width, float* __restrict__ out_a,
                                                                  float* __restrict__ out_b, int half) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= width) return;
+  __shared__ float red[8][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int b = 0; b < n_blocks; ++b) s = __fadd_rn(s, partials[(int64_t)b * width + j]);
-  if (j < half) out_a[j] = s;
-  else out_b[j - half] = s;
+  if (j < width)
+    for (int b = warp; b < n_blocks; b += 8) s = __fadd_rn(s, partials[(int64_t)b * width + j]);
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && j < width) {
+    float t = red[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t = __fadd_rn(t, red[w][lane]);
+    if (j < half) out_a[j] = t;
+    else out_b[j - half] = t;
+  }
 }
 
 // Weight-gradient fold: out_row_block[r][c] = sum over splits (ascending) of part[s][m][c].
@@ -628,7 +711,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     kern<<<(unsigned)(B * tiles), 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out,
                                                        NN, tiles);
     TPF_LAUNCH_OK();
-    trimul_colsum_fold_kernel<<<(2 * C + 255) / 256, 256, 0, stream>>>(w.part_ln_out, w.blocks_ln_out, 2 * C, d_gout,
+    trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 256, 0, stream>>>(w.part_ln_out, w.blocks_ln_out, 2 * C, d_gout,
                                                                        d_bout, C);
     TPF_LAUNCH_OK();
   }
@@ -674,7 +757,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     trimul_ln_bwd_kernel<C><<<w.blocks_ln_in, 256, 0, stream>>>(d_zln, z, gin, mean_in, rstd_in, d_z, w.part_ln_in, R,
                                                                 w.rows_per_block_in);
     TPF_LAUNCH_OK();
-    trimul_colsum_fold_kernel<<<(2 * C + 255) / 256, 256, 0, stream>>>(w.part_ln_in, w.blocks_ln_in, 2 * C, d_gin,
+    trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 256, 0, stream>>>(w.part_ln_in, w.blocks_ln_in, 2 * C, d_gin,
                                                                        d_bin, C);
     TPF_LAUNCH_OK();
   }
