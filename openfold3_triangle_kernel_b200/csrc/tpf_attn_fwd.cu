@@ -8,13 +8,14 @@
 // same math and rounding points (fp32 running max / sum, probabilities rounded to bf16 for P V,
 // fully masked rows give out = 0 and lse = -inf), different machine mapping:
 //
-//  * persistent CTAs, 10 warps.  A work item is (b, h, 128-query tile, PAIR of outer rows o);
+//  * persistent CTAs, 18 working warps.  A work item is (b, h, 128-query tile, PAIR of outer rows o);
 //    both rows of the pair use the same 128x128 bias tiles, so the bias - the largest
 //    operand stream - is fetched once per pair.
-//  * warps 0-3 / 4-7: two softmax groups, one per outer row, one thread per query row
-//    (= one TMEM lane).  warp 8: TMA producer.  warp 9: UMMA issuer.
+//  * warps 0-7 / 8-15: two softmax groups, one per outer row; two threads per query row
+//    (= TMEM lane), each owning 64 of the 128 keys of a tile, with packed fp32x2 arithmetic.
+//    warp 16: TMA producer.  warp 17: UMMA issuer.
 //  * Q K^T and P V run on tcgen05 with accumulators in TMEM.  The softmax group pulls the
-//    128 logits of its row into registers at once, releases the TMEM tile (so the next
+//    logits of its rows into registers at once, releases the TMEM tile (so the next
 //    Q K^T overlaps the exponentials), writes bf16 P into a swizzled smem tile for the
 //    P V UMMA, which accumulates the output in TMEM across key tiles; the accumulator
 //    is rescaled (TMEM load, multiply, store) only when a row maximum grows by more than
@@ -49,7 +50,7 @@ struct AttnFwdCfg {
   static constexpr int D = D_, NKV = NKV_;
   static constexpr int SWZ = 2 * D;              // bytes per smem row of a Q/K/V tile
   static constexpr int TILE = 128 * D * 2;       // one Q, K or V tile
-  static constexpr int NB = 2;                   // bias stages
+  static constexpr int NB = D <= 32 ? 2 : 1;     // bias stages
   static constexpr int BIAS_STAGE = 128 * 128 * 2;
   static constexpr int P_BYTES = 128 * 128 * 2;
   static constexpr int OFF_BIAS = 0;
@@ -58,18 +59,21 @@ struct AttnFwdCfg {
   static constexpr int OFF_V = OFF_K + 2 * NKV * TILE;           // [2][NKV]
   static constexpr int OFF_P = OFF_V + 2 * NKV * TILE;           // [2]
   static constexpr int OFF_MASK = OFF_P + 2 * P_BYTES;           // [2][NKV] x 512 B
-  static constexpr int OFF_BAR = OFF_MASK + 2 * NKV * 512;
+  static constexpr int OFF_XCHG = OFF_MASK + 2 * NKV * 512;      // [2 parity][2 groups][2 halves][128] fp32
+  static constexpr int OFF_BAR = OFF_XCHG + 2 * 2 * 2 * 128 * 4;
   static constexpr int N_BAR = 2 * NB + 2 * (2 + 4 * NKV + 4);
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
   static constexpr int TM_S = 0;      // S[w] at 128*w
   static constexpr int TM_O = 256;    // O[w] at 256 + 64*w
   static constexpr int TMEM_COLS = 512;
+  static constexpr int THREADS = 640;            // 16 softmax warps, TMA warp, UMMA warp, 2 idle
+  static constexpr int WARP_TMA = 16, WARP_MMA = 17;
   static_assert(D == 16 || D == 32 || D == 64, "head dim lanes");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
 template <class Cfg>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
                 const __grid_constant__ CUtensorMap tmMask, const AttnFwdParams p, int* __restrict__ status) {
@@ -101,7 +105,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     for (int s = 0; s < NB; ++s) {
       mbar_init(&b_full[s], 1);
-      mbar_init(&b_empty[s], 8);
+      mbar_init(&b_empty[s], 16);
     }
     for (int w = 0; w < 2; ++w) {
       mbar_init(q_full(w), 1);
@@ -113,8 +117,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(v_empty(w, s), 1);
       }
       mbar_init(s_full(w), 1);
-      mbar_init(s_free(w), 4);
-      mbar_init(p_ready(w), 4);
+      mbar_init(s_free(w), 8);
+      mbar_init(p_ready(w), 8);
       mbar_init(pv_done(w), 1);
     }
     *abort_flag = 0;
@@ -125,7 +129,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tma_prefetch_desc(&tmBias);
     tma_prefetch_desc(&tmMask);
   }
-  if (warp == 9) {
+  if (warp == Cfg::WARP_MMA) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -146,7 +150,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     b = r / p.H;
   };
 
-  if (warp == 8) {
+  if (warp == Cfg::WARP_TMA) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t q_ph[2] = {1, 1};
@@ -205,7 +209,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == Cfg::WARP_MMA) {
     // ------------------------------------------------------------------ UMMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
@@ -275,19 +279,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
-  } else {
-    // ------------------------------------------------------------------ softmax groups
-    const int w = warp >> 2;
-    const int row = 32 * (warp & 3) + lane;  // query row inside the tile == TMEM lane
-    const uint32_t t_s = tmem_addr(tmem_base, 32 * (warp & 3), Cfg::TM_S + 128 * w);
-    const uint32_t t_o = tmem_addr(tmem_base, 32 * (warp & 3), Cfg::TM_O + 64 * w);
-    uint8_t* p_tile = smem + Cfg::OFF_P + w * Cfg::P_BYTES;
+  } else if (warp < 16) {
+    // ------------------------------------------------------------------ softmax warps
+    // Two groups of 8 warps (one per outer row of the pair).  Inside a group, warps q and q+4
+    // share the 32 query rows of TMEM lane quarter q and split the 128 keys of a tile in two
+    // halves; they agree on the row maximum through a 64-thread named barrier.
+    const int w = warp >> 3;
+    const int hf = (warp >> 2) & 1;
+    const int qd = warp & 3;
+    const int row = 32 * qd + lane;  // query row inside the tile == TMEM lane
+    constexpr int DH = D / 2;        // output columns per thread
+    const uint32_t t_s = tmem_addr(tmem_base, 32 * qd, Cfg::TM_S + 128 * w + 64 * hf);
+    const uint32_t t_o = tmem_addr(tmem_base, 32 * qd, Cfg::TM_O + 64 * w + DH * hf);
+    uint8_t* p_row = smem + Cfg::OFF_P + w * Cfg::P_BYTES + hf * 16384 + row * 128;
+    float* xchg = reinterpret_cast<float*>(smem + Cfg::OFF_XCHG);
+    const int pair_bar = 1 + w * 4 + qd;
     constexpr float kLog2e = 1.4426950408889634f;
     constexpr float kLn2 = 0.6931471805599453f;
     const float scale = p.scale;
+    const uint64_t scale2 = f2_pack(scale, scale);
+    const uint64_t log2e2 = f2_pack(kLog2e, kLog2e);
 
     uint32_t sfull_ph = 0, pv_ph = 0, b_ph = 0, v_ph = 0;
-    int b_s = 0, v_s = 0;
+    int b_s = 0, v_s = 0, par = 0;
+
+    // value held by the partner thread (same row, other key half)
+    auto exchange = [&](float mine) -> float {
+      xchg[((par * 2 + w) * 2 + hf) * 128 + row] = mine;
+      named_barrier_sync(pair_bar, 64);
+      const float other = xchg[((par * 2 + w) * 2 + (hf ^ 1)) * 128 + row];
+      par ^= 1;
+      return other;
+    };
 
     for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
       int b, h, qt, o2;
@@ -307,65 +330,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         continue;
       }
 
-      // Running reference max (natural-log units) and row sum.  The output accumulates in
-      // TMEM across key tiles; it is rescaled only when the row max grows by more than
-      // kRescaleGap, so the common case costs no TMEM round trip.
-      float m_ref = -INFINITY, l_run = 0.f;
+      // Running reference max (natural-log units) and this thread's share of the row sum.  The
+      // output accumulates in TMEM across key tiles; it is rescaled only when the row max grows
+      // by more than kRescaleGap, so the common case costs no TMEM round trip.
+      float m_ref = -INFINITY, l_part = 0.f;
       constexpr float kRescaleGap = 5.0f;
 
       for (int j = 0; j < KT; ++j) {
-        float s[128];
+        uint64_t s2[32];  // 64 logits as fp32 pairs
         mbar_wait(s_full(w), sfull_ph, wctx);
         sfull_ph ^= 1;
         mbar_wait(v_full(w, v_s), v_ph, wctx);  // mask row travels with V
         mbar_wait(&b_full[b_s], b_ph, wctx);
         tc_fence_after();
-
-        const uint8_t* bias_tile = smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE;
-        const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_MASK + (w * NKV + v_s) * 512);
-        const bool tail = (j + 1) * 128 > p.N;
-        // all 128 logits of the row: four TMEM loads in flight, one wait
         {
-          uint32_t(*raw)[32] = reinterpret_cast<uint32_t(*)[32]>(s);
-          tmem_ld32(t_s + 0, raw[0]);
+          uint32_t(*raw)[32] = reinterpret_cast<uint32_t(*)[32]>(s2);
+          tmem_ld32(t_s, raw[0]);
           tmem_ld32(t_s + 32, raw[1]);
-          tmem_ld32(t_s + 64, raw[2]);
-          tmem_ld32(t_s + 96, raw[3]);
           tmem_ld_wait();
         }
+        const uint8_t* bias_row = smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE + hf * 16384 + row * 128;
+        const float* mask_row =
+            reinterpret_cast<const float*>(smem + Cfg::OFF_MASK + (w * NKV + v_s) * 512) + 64 * hf;
+        const bool tail = (j + 1) * 128 > p.N;
         float tmax4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {  // 16 key columns per step
-          // bias: 16 bf16 of this row = 2 x 16 B in the 128-byte-swizzled half tile
-          const uint8_t* brow = bias_tile + (c >> 2) * 16384 + row * 128;
-          uint4 bv[2];
+        for (int u = 0; u < 8; ++u) {  // 8 key columns per step
+          const uint4 bv = *reinterpret_cast<const uint4*>(bias_row + ((u ^ (row & 7)) << 4));
+          const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+          const ulonglong2 mkA = *reinterpret_cast<const ulonglong2*>(mask_row + 8 * u);
+          const ulonglong2 mkB = *reinterpret_cast<const ulonglong2*>(mask_row + 8 * u + 4);
+          const uint64_t mk2[4] = {mkA.x, mkA.y, mkB.x, mkB.y};
 #pragma unroll
-          for (int u = 0; u < 2; ++u)
-            bv[u] = *reinterpret_cast<const uint4*>(brow + ((((c & 3) * 2 + u) ^ (row & 7)) << 4));
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const uint32_t bw[4] = {bv[u].x, bv[u].y, bv[u].z, bv[u].w};
-            const float4 mk0 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u);
-            const float4 mk1 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u + 4);
-            const float mk[8] = {mk0.x, mk0.y, mk0.z, mk0.w, mk1.x, mk1.y, mk1.z, mk1.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float b_lo = __uint_as_float(bw[e] << 16);
-              const float b_hi = __uint_as_float(bw[e] & 0xFFFF0000u);
-              const int i0 = 16 * c + 8 * u + 2 * e;
-              float v0 = fmaf(s[i0], scale, b_lo) + mk[2 * e];
-              float v1 = fmaf(s[i0 + 1], scale, b_hi) + mk[2 * e + 1];
-              if (tail) {
-                if (j * 128 + i0 >= p.N) v0 = -INFINITY;
-                if (j * 128 + i0 + 1 >= p.N) v1 = -INFINITY;
-              }
-              s[i0] = v0;
-              s[i0 + 1] = v1;
-              tmax4[e] = fmaxf(tmax4[e], fmaxf(v0, v1));
+          for (int e = 0; e < 4; ++e) {
+            const uint64_t b2 = f2_pack_bits(bw[e] << 16, bw[e] & 0xFFFF0000u);
+            uint64_t v2 = f2_add(f2_fma(s2[4 * u + e], scale2, b2), mk2[e]);
+            float v0, v1;
+            f2_unpack(v2, v0, v1);
+            if (tail) {
+              const int k0 = j * 128 + 64 * hf + 8 * u + 2 * e;
+              if (k0 >= p.N) v0 = -INFINITY;
+              if (k0 + 1 >= p.N) v1 = -INFINITY;
+              v2 = f2_pack(v0, v1);
             }
+            s2[4 * u + e] = v2;
+            tmax4[e] = max3(tmax4[e], v0, v1);
           }
         }
-        const float tmax = fmaxf(fmaxf(tmax4[0], tmax4[1]), fmaxf(tmax4[2], tmax4[3]));
         // S, the bias tile and the mask row now live in registers
         tc_fence_before();
         __syncwarp();
@@ -382,7 +393,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           v_ph ^= 1;
         }
 
-        const float m_new = fmaxf(m_ref, tmax);
+        const float tmax = fmaxf(fmaxf(tmax4[0], tmax4[1]), fmaxf(tmax4[2], tmax4[3]));
+        const float m_new = max3(m_ref, tmax, exchange(tmax));
         if (j == 0) {
           m_ref = m_new;
         } else {
@@ -393,70 +405,71 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (__any_sync(0xffffffffu, m_new > m_ref + kRescaleGap)) {
             const float f = (m_new == -INFINITY) ? 1.f : ex2_approx((m_ref - m_new) * kLog2e);
 #pragma unroll
-            for (int c = 0; c < D; c += 16) {
-              uint32_t ro[16];
-              tmem_ld16(t_o + c, ro);
+            for (int c = 0; c < DH; c += 8) {
+              uint32_t ro[8];
+              tmem_ld8(t_o + c, ro);
               tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 16; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * f);
-              tmem_st16(t_o + c, ro);
+              for (int i = 0; i < 8; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * f);
+              tmem_st8(t_o + c, ro);
             }
             tmem_st_wait();
-            l_run *= f;
+            l_part *= f;
             m_ref = m_new;
           }
         }
-        const float neg_m2 = (m_ref == -INFINITY) ? 0.f : -m_ref * kLog2e;
+        const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * kLog2e;
+        const uint64_t neg_m2 = f2_pack(neg_m, neg_m);
 
-        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint64_t rs2[2] = {0ull, 0ull};  // two packed partial sums (bit pattern of +0.f pairs)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint8_t* prow = p_tile + (c >> 1) * 16384 + row * 128;
+        for (int u = 0; u < 8; ++u) {
+          uint32_t pk[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float e[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              e[i] = ex2_approx(fmaf(s[32 * c + 8 * u + i], kLog2e, neg_m2));
-              rs4[i & 3] += e[i];
-            }
-            uint4 pk;
-            pk.x = pack_bf16x2(e[0], e[1]);
-            pk.y = pack_bf16x2(e[2], e[3]);
-            pk.z = pack_bf16x2(e[4], e[5]);
-            pk.w = pack_bf16x2(e[6], e[7]);
-            *reinterpret_cast<uint4*>(prow + ((((c & 1) * 4 + u) ^ (row & 7)) << 4)) = pk;
+          for (int e = 0; e < 4; ++e) {
+            float a0, a1;
+            f2_unpack(f2_fma(s2[4 * u + e], log2e2, neg_m2), a0, a1);
+            const float e0 = ex2_approx(a0), e1 = ex2_approx(a1);
+            rs2[e & 1] = f2_add(rs2[e & 1], f2_pack(e0, e1));
+            pk[e] = pack_bf16x2(e0, e1);
           }
+          *reinterpret_cast<uint4*>(p_row + ((u ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
-        l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        {
+          float r0, r1, r2, r3;
+          f2_unpack(rs2[0], r0, r1);
+          f2_unpack(rs2[1], r2, r3);
+          l_part += (r0 + r1) + (r2 + r3);
+        }
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_ready(w));
       }
 
-      // last tile's P V, then the accumulated output
+      // last tile's P V, then this thread's half of the accumulated output columns
       mbar_wait(pv_done(w), pv_ph, wctx);
       pv_ph ^= 1;
       tc_fence_after();
-      float acc[D];
+      float acc[DH];
 #pragma unroll
-      for (int c = 0; c < D; c += 16) {
-        uint32_t ro[16];
-        tmem_ld16(t_o + c, ro);
+      for (int c = 0; c < DH; c += 8) {
+        uint32_t ro[8];
+        tmem_ld8(t_o + c, ro);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[c + i] = __uint_as_float(ro[i]);
+        for (int i = 0; i < 8; ++i) acc[c + i] = __uint_as_float(ro[i]);
       }
       tc_fence_before();
-      const float m_run = m_ref;
+      const float l_other = exchange(l_part);
+      const float l_run = hf == 0 ? l_part + l_other : l_other + l_part;
 
       const int q = qt * 128 + row;
       if (q < p.N) {
         const float inv = l_run > 0.f ? __fdividef(1.f, l_run) : 0.f;
-        __nv_bfloat16* orow = p.out + ((((int64_t)b * p.O + o) * p.N + q) * p.H + h) * D;
+        __nv_bfloat16* orow = p.out + ((((int64_t)b * p.O + o) * p.N + q) * p.H + h) * D + DH * hf;
 #pragma unroll
-        for (int c = 0; c < D; c += 8) {
+        for (int c = 0; c < DH; c += 8) {
           uint4 pk;
           pk.x = pack_bf16x2(acc[c + 0] * inv, acc[c + 1] * inv);
           pk.y = pack_bf16x2(acc[c + 2] * inv, acc[c + 3] * inv);
@@ -464,14 +477,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           pk.w = pack_bf16x2(acc[c + 6] * inv, acc[c + 7] * inv);
           *reinterpret_cast<uint4*>(orow + c) = pk;
         }
-        p.lse[(((int64_t)b * p.O + o) * p.H + h) * p.N + q] = l_run > 0.f ? m_run + log2f(l_run) * kLn2 : -INFINITY;
+        if (hf == 0)
+          p.lse[(((int64_t)b * p.O + o) * p.H + h) * p.N + q] =
+              l_run > 0.f ? m_ref + log2f(l_run) * kLn2 : -INFINITY;
       }
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == Cfg::WARP_MMA) {
     __syncwarp();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
@@ -518,7 +533,7 @@ int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
   }
   int grid = sm_count();
   if (grid > p.n_items) grid = p.n_items;
-  kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tb, tmk, p, status);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tb, tmk, p, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }

@@ -5,7 +5,7 @@
 // One CTA per SM walks a static list of (batch, m-tile, n-tile) output tiles.
 //   warp 0      : TMA producer  (one elected lane) - STAGES-deep smem ring
 //   warp 1      : UMMA issuer   (one elected lane) - accumulators double-buffered in TMEM
-//   warps 2..5  : epilogue      (128 threads = 128 TMEM lanes = 128 rows of the tile)
+//   warps 2..9  : epilogue      (two warps per 32 TMEM lanes = rows; alternate 32-column chunks)
 // Either operand may be K-major (k contiguous in memory) or MN-major (m / n
 // contiguous); the shared-memory tiles are written by TMA in the swizzled
 // canonical layouts the UMMA descriptors describe, so no thread touches them.
@@ -85,7 +85,7 @@ struct EpiStore {
 };
 
 template <class Cfg, class Epi>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmShape sh, const typename Epi::Params ep, int* __restrict__ status) {
   extern __shared__ uint8_t smem_dyn[];
@@ -118,7 +118,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 4);
+      mbar_init(&tempty[a], 8);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -214,7 +214,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
+    // 8 epilogue warps: two per TMEM lane quarter; they take alternate 32-column chunks
     const int lane_base = 32 * (warp & 3);
+    const int chunk_par = (warp - 2) >> 2;
     float* wsm = reinterpret_cast<float*>(epi_smem + (warp - 2) * Epi::kSmemPerWarp);
     int acc = 0;
     uint32_t acc_ph = 0;
@@ -228,36 +230,60 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t t_acc = tmem_addr(tmem_base, lane_base, acc * Cfg::ACC_STRIDE);
       const int m = m0 + lane_base + lane;
       if constexpr (!Epi::kPaired) {
-#pragma unroll 1
-        for (int c = 0; c < Cfg::BN; c += 32) {
-          uint32_t raw[32];
-          float v[32];
-          tmem_ld32(t_acc + c, raw);
-          tmem_ld_wait();
+        // all of this warp's 32-column chunks are requested before the single wait
+        constexpr int NCH = (Cfg::BN / 32 + 1) / 2;
+        uint32_t raw[NCH][32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-          if (n0 + c < sh.N) Epi::apply(ep, sh, b, m, n0 + c, v, wsm, lane);
+        for (int k = 0; k < NCH; ++k) {
+          const int c = 32 * chunk_par + 64 * k;
+          if (c < Cfg::BN) tmem_ld32(t_acc + c, raw[k]);
+        }
+        tmem_ld_wait();
+        // the accumulator now lives in registers: hand the TMEM buffer back before the epilogue math
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+          const int c = 32 * chunk_par + 64 * k;
+          if (c < Cfg::BN && n0 + c < sh.N) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[k][i]);
+            Epi::apply(ep, sh, b, m, n0 + c, v, wsm, lane);
+          }
         }
       } else {
         // Column c (first half of the tile) pairs with column c + BN/2.
-#pragma unroll 1
-        for (int c = 0; c < Cfg::BN / 2; c += 32) {
-          uint32_t raw0[32], raw1[32];
-          float v0[32], v1[32];
-          tmem_ld32(t_acc + c, raw0);
-          tmem_ld32(t_acc + Cfg::BN / 2 + c, raw1);
-          tmem_ld_wait();
+        constexpr int NCH = (Cfg::BN / 64 + 1) / 2;
+        uint32_t raw0[NCH][32], raw1[NCH][32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            v0[i] = __uint_as_float(raw0[i]);
-            v1[i] = __uint_as_float(raw1[i]);
+        for (int k = 0; k < NCH; ++k) {
+          const int c = 32 * chunk_par + 64 * k;
+          if (c < Cfg::BN / 2) {
+            tmem_ld32(t_acc + c, raw0[k]);
+            tmem_ld32(t_acc + Cfg::BN / 2 + c, raw1[k]);
           }
-          Epi::apply2(ep, sh, b, m, n0, c, v0, v1, wsm, lane);
+        }
+        tmem_ld_wait();
+        // the accumulator now lives in registers: hand the TMEM buffer back before the epilogue math
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+          const int c = 32 * chunk_par + 64 * k;
+          if (c < Cfg::BN / 2) {
+            float v0[32], v1[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              v0[i] = __uint_as_float(raw0[k][i]);
+              v1[i] = __uint_as_float(raw1[k][i]);
+            }
+            Epi::apply2(ep, sh, b, m, n0, c, v0, v1, wsm, lane);
+          }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
       if (++acc == 2) {
         acc = 0;
         acc_ph ^= 1;

@@ -3,7 +3,7 @@
 // matrix descriptors and the instruction descriptor for bf16 x bf16 -> fp32.
 //
 // Every wait in this file is bounded: a wait that does not complete within
-// TPF_WAIT_LIMIT_NS raises a per-CTA abort flag (all later waits of that CTA
+// TPF_WAIT_LIMIT_CYCLES SM cycles raises a per-CTA abort flag (all later waits of that CTA
 // return at once) and records a non-zero code in a global status word that the
 // host reads back through tpf_device_status().  Kernels therefore always run to
 // their normal end, free their TMEM and return.
@@ -16,8 +16,8 @@
 
 namespace tpf {
 
-#ifndef TPF_WAIT_LIMIT_NS
-#define TPF_WAIT_LIMIT_NS 2000000000ull
+#ifndef TPF_WAIT_LIMIT_CYCLES
+#define TPF_WAIT_LIMIT_CYCLES 4000000000ll
 #endif
 
 enum StatusCode : int {
@@ -69,14 +69,18 @@ struct WaitCtx {
   int* status;
 };
 
+// Bounded wait.  The common case (a few polls) touches no timer; after that the SM cycle
+// counter bounds the wait (TPF_WAIT_LIMIT_CYCLES, about two seconds at boost clock).
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
-  if (mbar_try_wait(bar, parity)) return;
-  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  for (int i = 0; i < 128; ++i)
+    if (mbar_try_wait(bar, parity)) return;
+  const long long t0 = clock64();
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (((++it) & 0x3F) == 0) {
+    if (((++it) & 0xFF) == 0) {
       if (*ctx.flag) return;
-      if (global_timer_ns() - t0 > TPF_WAIT_LIMIT_NS) {
+      if (clock64() - t0 > (long long)TPF_WAIT_LIMIT_CYCLES) {
         *ctx.flag = 1;
         atomicCAS(ctx.status, 0, (int)kStatusWaitTimeout);
         return;
@@ -234,6 +238,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -264,6 +273,44 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
   // 1 / (1 + 2^(-x log2 e))
   return __fdividef(1.0f, 1.0f + ex2_approx(-1.4426950408889634f * x));
 }
+// Packed fp32 pairs (sm_100 executes two fp32 FMAs / adds per instruction) and 3-input max.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_pack_bits(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

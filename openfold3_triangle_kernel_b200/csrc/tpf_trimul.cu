@@ -89,31 +89,42 @@ __global__ void __launch_bounds__(256) trimul_ln_fwd_kernel(const bf16* __restri
                                                             float* __restrict__ mean, float* __restrict__ rstd,
                                                             int64_t R) {
   using L = RowLanes<C>;
+  constexpr int G = 4;  // row groups per warp, all loads issued before the first use
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int sub = lane / L::LPR, part = lane % L::LPR;
-  const int64_t row = warp * L::RPW + sub;
-  const bool active = sub < L::RPW && row < R;
-  float x[4] = {0.f, 0.f, 0.f, 0.f};
-  if (active) {
-    const uint2 u = *reinterpret_cast<const uint2*>(z + row * C + part * 4);
-    x[0] = bf16_lo(u.x); x[1] = bf16_hi(u.x); x[2] = bf16_lo(u.y); x[3] = bf16_hi(u.y);
+  float4 g = make_float4(0.f, 0.f, 0.f, 0.f), b = g;
+  if (sub < L::RPW) {
+    g = *reinterpret_cast<const float4*>(gamma + part * 4);
+    b = *reinterpret_cast<const float4*>(beta + part * 4);
   }
-  const float s1 = group_sum<C>(x[0] + x[1] + x[2] + x[3]);
-  const float s2 = group_sum<C>(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
-  const float mu = s1 * (1.f / C);
-  const float var = fmaxf(s2 * (1.f / C) - mu * mu, 0.f);
-  const float rs = rsqrtf(var + 1e-5f);
-  if (active) {
-    const float4 g = *reinterpret_cast<const float4*>(gamma + part * 4);
-    const float4 b = *reinterpret_cast<const float4*>(beta + part * 4);
-    uint2 o;
-    o.x = pack_bf16x2((x[0] - mu) * rs * g.x + b.x, (x[1] - mu) * rs * g.y + b.y);
-    o.y = pack_bf16x2((x[2] - mu) * rs * g.z + b.z, (x[3] - mu) * rs * g.w + b.w);
-    *reinterpret_cast<uint2*>(zln + row * C + part * 4) = o;
-    if (part == 0) {
-      mean[row] = mu;
-      rstd[row] = rs;
+  uint2 u[G];
+  bool active[G];
+#pragma unroll
+  for (int r = 0; r < G; ++r) {
+    const int64_t row = (warp * G + r) * L::RPW + sub;
+    active[r] = sub < L::RPW && row < R;
+    u[r] = make_uint2(0u, 0u);
+    if (active[r]) u[r] = *reinterpret_cast<const uint2*>(z + row * C + part * 4);
+  }
+#pragma unroll
+  for (int r = 0; r < G; ++r) {
+    const int64_t row = (warp * G + r) * L::RPW + sub;
+    const float x[4] = {bf16_lo(u[r].x), bf16_hi(u[r].x), bf16_lo(u[r].y), bf16_hi(u[r].y)};
+    const float s1 = group_sum<C>(x[0] + x[1] + x[2] + x[3]);
+    const float s2 = group_sum<C>(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+    const float mu = s1 * (1.f / C);
+    const float var = fmaxf(s2 * (1.f / C) - mu * mu, 0.f);
+    const float rs = rsqrtf(var + 1e-5f);
+    if (active[r]) {
+      uint2 o;
+      o.x = pack_bf16x2((x[0] - mu) * rs * g.x + b.x, (x[1] - mu) * rs * g.y + b.y);
+      o.y = pack_bf16x2((x[2] - mu) * rs * g.z + b.z, (x[3] - mu) * rs * g.w + b.w);
+      *reinterpret_cast<uint2*>(zln + row * C + part * 4) = o;
+      if (part == 0) {
+        mean[row] = mu;
+        rstd[row] = rs;
+      }
     }
   }
 }
@@ -357,21 +368,22 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
                                                                const float* __restrict__ rstd, bf16* __restrict__ dx_cm,
                                                                float* __restrict__ partials, int64_t NN,
                                                                int tiles_per_batch) {
+  constexpr int TR = 32;  // rows per CTA (keeps 6 CTAs per SM resident)
   extern __shared__ float sm[];
-  float(*xh)[65] = reinterpret_cast<float(*)[65]>(sm);            // xhat [C][65]
-  float(*dg)[65] = reinterpret_cast<float(*)[65]>(sm + C * 65);   // d_xln [C][65]
-  __shared__ float s_m1[64], s_m2[64], s_rs[64], s_mu[64];
+  float(*xh)[TR + 1] = reinterpret_cast<float(*)[TR + 1]>(sm);                  // xhat [C][TR+1]
+  float(*dg)[TR + 1] = reinterpret_cast<float(*)[TR + 1]>(sm + C * (TR + 1));  // d_xln [C][TR+1]
+  __shared__ float s_m1[TR], s_m2[TR], s_rs[TR], s_mu[TR];
   const int bb = blockIdx.x / tiles_per_batch;
-  const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * 64;
-  if (threadIdx.x < 64) {
+  const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * TR;
+  if (threadIdx.x < TR) {
     const bool ok = r0 + threadIdx.x < NN;
     s_mu[threadIdx.x] = ok ? mean[(int64_t)bb * NN + r0 + threadIdx.x] : 0.f;
     s_rs[threadIdx.x] = ok ? rstd[(int64_t)bb * NN + r0 + threadIdx.x] : 0.f;
   }
   __syncthreads();
   // x (channel-major): 8 consecutive rows of one channel per 16-byte load
-  for (int idx = threadIdx.x; idx < C * 8; idx += 256) {
-    const int c = idx >> 3, j8 = idx & 7;
+  for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
+    const int c = idx / (TR / 8), j8 = idx % (TR / 8);
     uint4 u = make_uint4(0u, 0u, 0u, 0u);
     const bool ok = r0 + 8 * j8 < NN;
     if (ok) u = *reinterpret_cast<const uint4*>(x_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8);
@@ -384,7 +396,7 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
     }
   }
   // d_xln (row-major): 8 consecutive channels of one row per 16-byte load
-  for (int idx = threadIdx.x; idx < 64 * (C / 8); idx += 256) {
+  for (int idx = threadIdx.x; idx < TR * (C / 8); idx += 256) {
     const int j = idx / (C / 8), c8 = idx % (C / 8);
     uint4 u = make_uint4(0u, 0u, 0u, 0u);
     if (r0 + j < NN) u = *reinterpret_cast<const uint4*>(d_xln + ((int64_t)bb * NN + r0 + j) * C + 8 * c8);
@@ -397,7 +409,7 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int j = warp; j < 64; j += 8) {
+  for (int j = warp; j < TR; j += 8) {
     float a1 = 0.f, a2 = 0.f;
 #pragma unroll
     for (int c = lane; c < C; c += 32) {
@@ -416,8 +428,8 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < C * 8; idx += 256) {
-    const int c = idx >> 3, j8 = idx & 7;
+  for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
+    const int c = idx / (TR / 8), j8 = idx % (TR / 8);
     if (r0 + 8 * j8 >= NN) continue;
     const float gc = gamma[c];
     float v[8];
@@ -434,7 +446,7 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
   if (threadIdx.x < C) {
     const int c = threadIdx.x;
     float sg = 0.f, sb = 0.f;
-    for (int j = 0; j < 64; ++j) {
+    for (int j = 0; j < TR; ++j) {
       sg += dg[c][j] * xh[c][j];
       sb += dg[c][j];
     }
@@ -459,6 +471,7 @@ __global__ void __launch_bounds__(256) trimul_ln_bwd_kernel(const bf16* __restri
   float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f);
   if (sub < L::RPW) g4 = *reinterpret_cast<const float4*>(gamma + part * 4);
   float ag[4] = {0.f, 0.f, 0.f, 0.f}, ab[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
   for (int it = warp * L::RPW; it < rows_per_block; it += 8 * L::RPW) {
     const int64_t row = row_begin + it + sub;
     const bool active = sub < L::RPW && it + sub < rows_per_block && row < R;
@@ -513,22 +526,24 @@ __global__ void __launch_bounds__(256) trimul_ln_bwd_kernel(const bf16* __restri
 }
 
 // out[j] = fixed-order sum over blocks of partials[blk][j], j < width.  One CTA per 32 columns;
-// warp w adds blocks w, w+8, ... in ascending order, then the 8 warp sums are added in warp order.
-__global__ void __launch_bounds__(256) trimul_colsum_fold_kernel(const float* __restrict__ partials, int n_blocks,
+// warp w adds blocks w, w+32, ... in ascending order, then the 32 warp sums are added in warp order.
+__global__ void __launch_bounds__(1024) trimul_colsum_fold_kernel(const float* __restrict__ partials, int n_blocks,
                                                                  int width, float* __restrict__ out_a,
                                                                  float* __restrict__ out_b, int half) {
-  __shared__ float red[8][32];
+  __shared__ float red[32][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.x * 32 + lane;
   float s = 0.f;
-  if (j < width)
-    for (int b = warp; b < n_blocks; b += 8) s = __fadd_rn(s, partials[(int64_t)b * width + j]);
+  if (j < width) {
+#pragma unroll 4
+    for (int b = warp; b < n_blocks; b += 32) s = __fadd_rn(s, partials[(int64_t)b * width + j]);
+  }
   red[warp][lane] = s;
   __syncthreads();
   if (warp == 0 && j < width) {
     float t = red[0][lane];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) t = __fadd_rn(t, red[w][lane]);
+    for (int w = 1; w < 32; ++w) t = __fadd_rn(t, red[w][lane]);
     if (j < half) out_a[j] = t;
     else out_b[j - half] = t;
   }
@@ -544,6 +559,7 @@ __global__ void __launch_bounds__(256) trimul_wgrad_fold_kernel(const float* __r
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= M * C) return;
   float s = 0.f;
+#pragma unroll 8
   for (int k = 0; k < n_splits; ++k) s = __fadd_rn(s, part[(int64_t)k * M * C + i]);
   const int row = i / C, col = i % C;
   d.dst[row / C][(row % C) * C + col] = s;
@@ -585,7 +601,7 @@ static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk
   const int64_t NN = N * N, R = B * NN;
   using L = RowLanes<C>;
   {
-    const int64_t warps = (R + L::RPW - 1) / L::RPW;
+    const int64_t warps = (R + 4 * L::RPW - 1) / (4 * L::RPW);
     const int64_t blocks = (warps + 7) / 8;
     trimul_ln_fwd_kernel<C><<<(unsigned)blocks, 256, 0, stream>>>(z, gin, bin, zln, mean_in, rstd_in, R);
     TPF_LAUNCH_OK();
@@ -651,7 +667,7 @@ static void plan_bwd_workspace(int64_t B, int64_t N, int64_t C, char* base, Trim
   split_plan(R, 1, &w->splits_wz, &w->kps_wz);
   w->part_w5 = reinterpret_cast<float*>(take((int64_t)w->splits_w5 * 5 * C * C * 4));
   w->part_wz = reinterpret_cast<float*>(take((int64_t)w->splits_wz * C * C * 4));
-  w->blocks_ln_out = (int)(B * ((NN + 63) / 64));
+  w->blocks_ln_out = (int)(B * ((NN + 31) / 32));
   w->rows_per_block_in = 256;
   w->blocks_ln_in = (int)((R + 255) / 256);
   w->part_ln_out = reinterpret_cast<float*>(take((int64_t)w->blocks_ln_out * 2 * C * 4));
@@ -700,9 +716,9 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
   }
   // 3. output norm backward -> d_x (channel-major), d_gamma_out, d_beta_out
   {
-    const int tiles = (int)((NN + 63) / 64);
+    const int tiles = (int)((NN + 31) / 32);
     auto kern = trimul_xnorm_bwd_kernel<C>;
-    const int smem = 2 * C * 65 * 4;
+    const int smem = 2 * C * 33 * 4;
     static bool attr_done = false;
     if (!attr_done) {
       TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -711,7 +727,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     kern<<<(unsigned)(B * tiles), 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out,
                                                        NN, tiles);
     TPF_LAUNCH_OK();
-    trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 256, 0, stream>>>(w.part_ln_out, w.blocks_ln_out, 2 * C, d_gout,
+    trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(w.part_ln_out, w.blocks_ln_out, 2 * C, d_gout,
                                                                        d_bout, C);
     TPF_LAUNCH_OK();
   }
@@ -757,7 +773,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     trimul_ln_bwd_kernel<C><<<w.blocks_ln_in, 256, 0, stream>>>(d_zln, z, gin, mean_in, rstd_in, d_z, w.part_ln_in, R,
                                                                 w.rows_per_block_in);
     TPF_LAUNCH_OK();
-    trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 256, 0, stream>>>(w.part_ln_in, w.blocks_ln_in, 2 * C, d_gin,
+    trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(w.part_ln_in, w.blocks_ln_in, 2 * C, d_gin,
                                                                        d_bin, C);
     TPF_LAUNCH_OK();
   }
