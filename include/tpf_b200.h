@@ -181,6 +181,41 @@ int tpf_trimul_bwd(const void* d_out, const void* z, const float* mask,
                    float* d_norm_in_w, float* d_norm_in_b, float* d_norm_out_w, float* d_norm_out_b,
                    void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Stage-wise TriMul for row-sharded (axially parallel) execution.  `rows_per_batch` is the number of
+ * pair rows each batch entry holds on this rank (N_local * N; 0 means N * N; a multiple of 64) and
+ * replaces N*N in every [B*N*N, C] / [B*C, N*N] extent above.  `stages` selects
+ *   forward : 1 = LayerNorm + projections + gating (z -> zln, a_cm, b_cm, gate, statistics)
+ *             2 = k-contraction (whole pair tensors only; sharded callers run tpf_bmm_bf16 on their
+ *                 channel shard between two all-to-alls instead)
+ *             4 = output LayerNorm + projection + gate (x_cm, gate -> out, xln, statistics)
+ *   backward: 1 = output gate / projection / LayerNorm backward (-> dx_cm, d_p_out, d_norm_out_*)
+ *             2 = contraction backward (dx_cm, a_cm, b_cm -> da_cm, db_cm)
+ *             4 = projection / input LayerNorm backward (da_cm, db_cm -> d_z, d_p_in, d_g_in, d_g_out, d_norm_in_*)
+ * Backward stages 1 and 4 communicate through `workspace`: pass the same buffer to both calls
+ * (size: tpf_trimul_bwd_stages_workspace_bytes).  dx_cm / da_cm / db_cm, when not NULL, are used
+ * instead of the workspace's own buffers so the caller can exchange them between ranks.
+ * The reference has no sharded TriMul; these follow the stage split of
+ * openfold3/core/kernels/turbopairformer/turbopairformer_trimul.py:225-263, 327-392. */
+int64_t tpf_trimul_bwd_stages_workspace_bytes(int64_t B, int64_t rows_per_batch, int64_t C);
+int tpf_trimul_fwd_stages(const void* z, const float* mask,
+                   const float* p_in, const float* g_in, const float* p_out, const float* g_out,
+                   const float* norm_in_w, const float* norm_in_b, const float* norm_out_w, const float* norm_out_b,
+                   int direction, int64_t B, int64_t N, int64_t C,
+                   void* out, void* zln, float* mean_in, float* rstd_in, void* a_cm, void* b_cm, void* gate,
+                   void* x_cm, void* xln, float* mean_out, float* rstd_out,
+                   void* workspace, int64_t workspace_bytes, int64_t rows_per_batch, int stages, void* stream);
+int tpf_trimul_bwd_stages(const void* d_out, const void* z, const float* mask,
+                   const float* p_in, const float* g_in, const float* p_out, const float* g_out,
+                   const float* norm_in_w, const float* norm_out_w,
+                   int direction, int64_t B, int64_t N, int64_t C,
+                   const void* out, const void* zln, const float* mean_in, const float* rstd_in,
+                   const void* a_cm, const void* b_cm, const void* gate, const void* x_cm, const void* xln,
+                   const float* mean_out, const float* rstd_out,
+                   void* d_z, float* d_p_in, float* d_g_in, float* d_p_out, float* d_g_out,
+                   float* d_norm_in_w, float* d_norm_in_b, float* d_norm_out_w, float* d_norm_out_b,
+                   void* workspace, int64_t workspace_bytes, int64_t rows_per_batch, int stages,
+                   void* dx_cm, void* da_cm, void* db_cm, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -36,10 +36,14 @@ SIGNATURES = {
                      _I, _I, _I, _I, _I, _f, _P],
     "tpf_trimul_fwd_workspace_bytes": [_I, _I, _I],
     "tpf_trimul_bwd_workspace_bytes": [_I, _I, _I],
+    "tpf_trimul_bwd_stages_workspace_bytes": [_I, _I, _I],
+    "tpf_trimul_fwd_stages": [_P] * 10 + [_i, _I, _I, _I] + [_P] * 12 + [_I, _I, _i, _P],
+    "tpf_trimul_bwd_stages": [_P] * 9 + [_i, _I, _I, _I] + [_P] * 21 + [_I, _I, _i, _P, _P, _P, _P],
     "tpf_trimul_fwd": [_P] * 10 + [_i, _I, _I, _I] + [_P] * 12 + [_I, _P],
     "tpf_trimul_bwd": [_P] * 9 + [_i, _I, _I, _I] + [_P] * 21 + [_I, _P],
 }
 _RESTYPES = {"tpf_trimul_fwd_workspace_bytes": ctypes.c_int64, "tpf_trimul_bwd_workspace_bytes": ctypes.c_int64,
+             "tpf_trimul_bwd_stages_workspace_bytes": ctypes.c_int64,
              "tpf_attn_bwd_workspace_bytes": ctypes.c_int64, "tpf_version": ctypes.c_char_p, "tpf_last_error_string": ctypes.c_char_p}
 
 ERROR_NAMES = {1: "invalid argument", 2: "unsupported", 3: "CUDA error", 4: "workspace", 5: "device status"}

@@ -47,14 +47,15 @@ int trimul_fwd(const void* z, const float* mask, const float* p_in, const float*
                const float* g_out, const float* gin, const float* bin, const float* gout, const float* bout,
                int incoming, int64_t B, int64_t N, int64_t C, void* out, void* zln, float* mean_in, float* rstd_in,
                void* a_cm, void* b_cm, void* gate, void* x_cm, void* xln, float* mean_out, float* rstd_out,
-               void* workspace, int64_t workspace_bytes, cudaStream_t stream);
+               void* workspace, int64_t workspace_bytes, int64_t NN, int stages, cudaStream_t stream);
 int trimul_bwd(const void* d_out, const void* z, const float* mask, const float* p_in, const float* g_in,
                const float* p_out, const float* g_out, const float* gin, const float* gout, int incoming, int64_t B,
                int64_t N, int64_t C, const void* out, const void* zln, const float* mean_in, const float* rstd_in,
                const void* a_cm, const void* b_cm, const void* gate, const void* x_cm, const void* xln,
                const float* mean_out, const float* rstd_out, void* d_z, float* d_p_in, float* d_g_in, float* d_p_out,
                float* d_g_out, float* d_gin, float* d_bin, float* d_gout, float* d_bout, void* workspace,
-               int64_t workspace_bytes, cudaStream_t stream);
+               int64_t workspace_bytes, int64_t NN, int stages, void* dx_io, void* da_io, void* db_io,
+               cudaStream_t stream);
 
 }  // namespace tpf
 
@@ -172,7 +173,24 @@ int64_t tpf_trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C) {
 }
 
 int64_t tpf_trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C) {
-  return trimul_shape_ok(B, N, C) ? tpf::trimul_bwd_workspace_bytes(B, N, C) : 0;
+  return trimul_shape_ok(B, N, C) ? tpf::trimul_bwd_workspace_bytes(B, N * N, C) : 0;
+}
+
+int64_t tpf_trimul_bwd_stages_workspace_bytes(int64_t B, int64_t rows_per_batch, int64_t C) {
+  return (trimul_shape_ok(B, 8, C) && rows_per_batch > 0) ? tpf::trimul_bwd_workspace_bytes(B, rows_per_batch, C) : 0;
+}
+
+int tpf_trimul_fwd_stages(const void* z, const float* mask, const float* p_in, const float* g_in, const float* p_out,
+                          const float* g_out, const float* norm_in_w, const float* norm_in_b, const float* norm_out_w,
+                          const float* norm_out_b, int direction, int64_t B, int64_t N, int64_t C, void* out, void* zln,
+                          float* mean_in, float* rstd_in, void* a_cm, void* b_cm, void* gate, void* x_cm, void* xln,
+                          float* mean_out, float* rstd_out, void* workspace, int64_t workspace_bytes,
+                          int64_t rows_per_batch, int stages, void* stream) {
+  TPF_REQUIRE(direction == 0 || direction == 1, TPF_ERR_INVALID_ARGUMENT,
+              "tpf_trimul_fwd: direction must be 0 (outgoing) or 1 (incoming)");
+  return tpf::trimul_fwd(z, mask, p_in, g_in, p_out, g_out, norm_in_w, norm_in_b, norm_out_w, norm_out_b, direction, B,
+                         N, C, out, zln, mean_in, rstd_in, a_cm, b_cm, gate, x_cm, xln, mean_out, rstd_out, workspace,
+                         workspace_bytes, rows_per_batch, stages, static_cast<cudaStream_t>(stream));
 }
 
 int tpf_trimul_fwd(const void* z, const float* mask, const float* p_in, const float* g_in, const float* p_out,
@@ -180,11 +198,27 @@ int tpf_trimul_fwd(const void* z, const float* mask, const float* p_in, const fl
                    const float* norm_out_b, int direction, int64_t B, int64_t N, int64_t C, void* out, void* zln,
                    float* mean_in, float* rstd_in, void* a_cm, void* b_cm, void* gate, void* x_cm, void* xln,
                    float* mean_out, float* rstd_out, void* workspace, int64_t workspace_bytes, void* stream) {
+  return tpf_trimul_fwd_stages(z, mask, p_in, g_in, p_out, g_out, norm_in_w, norm_in_b, norm_out_w, norm_out_b,
+                               direction, B, N, C, out, zln, mean_in, rstd_in, a_cm, b_cm, gate, x_cm, xln, mean_out,
+                               rstd_out, workspace, workspace_bytes, 0, 7, stream);
+}
+
+int tpf_trimul_bwd_stages(const void* d_out, const void* z, const float* mask, const float* p_in, const float* g_in,
+                          const float* p_out, const float* g_out, const float* norm_in_w, const float* norm_out_w,
+                          int direction, int64_t B, int64_t N, int64_t C, const void* out, const void* zln,
+                          const float* mean_in, const float* rstd_in, const void* a_cm, const void* b_cm,
+                          const void* gate, const void* x_cm, const void* xln, const float* mean_out,
+                          const float* rstd_out, void* d_z, float* d_p_in, float* d_g_in, float* d_p_out,
+                          float* d_g_out, float* d_norm_in_w, float* d_norm_in_b, float* d_norm_out_w,
+                          float* d_norm_out_b, void* workspace, int64_t workspace_bytes, int64_t rows_per_batch,
+                          int stages, void* dx_cm, void* da_cm, void* db_cm, void* stream) {
   TPF_REQUIRE(direction == 0 || direction == 1, TPF_ERR_INVALID_ARGUMENT,
-              "tpf_trimul_fwd: direction must be 0 (outgoing) or 1 (incoming)");
-  return tpf::trimul_fwd(z, mask, p_in, g_in, p_out, g_out, norm_in_w, norm_in_b, norm_out_w, norm_out_b, direction, B,
-                         N, C, out, zln, mean_in, rstd_in, a_cm, b_cm, gate, x_cm, xln, mean_out, rstd_out, workspace,
-                         workspace_bytes, static_cast<cudaStream_t>(stream));
+              "tpf_trimul_bwd: direction must be 0 (outgoing) or 1 (incoming)");
+  return tpf::trimul_bwd(d_out, z, mask, p_in, g_in, p_out, g_out, norm_in_w, norm_out_w, direction, B, N, C, out, zln,
+                         mean_in, rstd_in, a_cm, b_cm, gate, x_cm, xln, mean_out, rstd_out, d_z, d_p_in, d_g_in,
+                         d_p_out, d_g_out, d_norm_in_w, d_norm_in_b, d_norm_out_w, d_norm_out_b, workspace,
+                         workspace_bytes, rows_per_batch, stages, dx_cm, da_cm, db_cm,
+                         static_cast<cudaStream_t>(stream));
 }
 
 int tpf_trimul_bwd(const void* d_out, const void* z, const float* mask, const float* p_in, const float* g_in,
@@ -195,12 +229,10 @@ int tpf_trimul_bwd(const void* d_out, const void* z, const float* mask, const fl
                    float* d_p_in, float* d_g_in, float* d_p_out, float* d_g_out, float* d_norm_in_w,
                    float* d_norm_in_b, float* d_norm_out_w, float* d_norm_out_b, void* workspace,
                    int64_t workspace_bytes, void* stream) {
-  TPF_REQUIRE(direction == 0 || direction == 1, TPF_ERR_INVALID_ARGUMENT,
-              "tpf_trimul_bwd: direction must be 0 (outgoing) or 1 (incoming)");
-  return tpf::trimul_bwd(d_out, z, mask, p_in, g_in, p_out, g_out, norm_in_w, norm_out_w, direction, B, N, C, out, zln,
-                         mean_in, rstd_in, a_cm, b_cm, gate, x_cm, xln, mean_out, rstd_out, d_z, d_p_in, d_g_in,
-                         d_p_out, d_g_out, d_norm_in_w, d_norm_in_b, d_norm_out_w, d_norm_out_b, workspace,
-                         workspace_bytes, static_cast<cudaStream_t>(stream));
+  return tpf_trimul_bwd_stages(d_out, z, mask, p_in, g_in, p_out, g_out, norm_in_w, norm_out_w, direction, B, N, C, out,
+                               zln, mean_in, rstd_in, a_cm, b_cm, gate, x_cm, xln, mean_out, rstd_out, d_z, d_p_in,
+                               d_g_in, d_p_out, d_g_out, d_norm_in_w, d_norm_in_b, d_norm_out_w, d_norm_out_b,
+                               workspace, workspace_bytes, 0, 7, nullptr, nullptr, nullptr, stream);
 }
 
 }  // extern "C"

@@ -595,32 +595,32 @@ static int proj_gemm(const bf16* zln, const bf16* W5, int64_t R, int n_cols, con
 
 template <int C>
 static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk, const float* gin, const float* bin,
-                        const float* gout, const float* bout, int incoming, int64_t B, int64_t N, bf16* out, bf16* zln,
-                        float* mean_in, float* rstd_in, bf16* a_cm, bf16* b_cm, bf16* gate, bf16* x_cm, bf16* xln,
-                        float* mean_out, float* rstd_out, int* status, cudaStream_t stream) {
-  const int64_t NN = N * N, R = B * NN;
+                        const float* gout, const float* bout, int incoming, int64_t B, int64_t N, int64_t NN,
+                        int stages, bf16* out, bf16* zln, float* mean_in, float* rstd_in, bf16* a_cm, bf16* b_cm,
+                        bf16* gate, bf16* x_cm, bf16* xln, float* mean_out, float* rstd_out, int* status,
+                        cudaStream_t stream) {
+  // NN = pair rows per batch entry (N*N for a whole pair tensor, N_local*N for a row shard)
+  const int64_t R = B * NN;
   using L = RowLanes<C>;
-  {
+  int rc = TPF_OK;
+  if (stages & 1) {
     const int64_t warps = (R + 4 * L::RPW - 1) / (4 * L::RPW);
     const int64_t blocks = (warps + 7) / 8;
     trimul_ln_fwd_kernel<C><<<(unsigned)blocks, 256, 0, stream>>>(z, gin, bin, zln, mean_in, rstd_in, R);
     TPF_LAUNCH_OK();
-  }
-  int rc;
-  {
     EpiProjGate::Params ep{a_cm, b_cm, gate, mask, C, NN};
     if ((rc = proj_gemm<C, EpiProjGate>(zln, pk.W5, R, 5 * C, ep, status, stream))) return rc;
   }
-  // k-contraction: batch = B*C problems of N x N x N
-  rc = bmm_bf16(a_cm, N, NN, incoming, b_cm, N, NN, incoming, x_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream);
-  if (rc) return rc;
-  {
+  if (stages & 2) {
+    // k-contraction: batch = B*C problems of N x N x N
+    rc = bmm_bf16(a_cm, N, NN, incoming, b_cm, N, NN, incoming, x_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream);
+    if (rc) return rc;
+  }
+  if (stages & 4) {
     const int tiles = (int)((NN + 63) / 64);
     trimul_xnorm_fwd_kernel<C><<<(unsigned)(B * tiles), 256, 0, stream>>>(x_cm, gout, bout, xln, mean_out, rstd_out,
                                                                           NN, tiles);
     TPF_LAUNCH_OK();
-  }
-  {
     using Cfg = GemmCfg<128, C, 128, false, 128, false, 4>;
     GemmShape sh{(int)R, C, C, 1, 0};
     EpiOutGate::Params ep{out, gate, C};
@@ -648,8 +648,8 @@ struct TrimulBwdWorkspace {
 
 static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
-static void plan_bwd_workspace(int64_t B, int64_t N, int64_t C, char* base, TrimulBwdWorkspace* w) {
-  const int64_t NN = N * N, R = B * NN;
+static void plan_bwd_workspace(int64_t B, int64_t NN, int64_t C, char* base, TrimulBwdWorkspace* w) {
+  const int64_t R = B * NN;
   int64_t off = 0;
   auto take = [&](int64_t bytes) {
     char* p = base ? base + off : nullptr;
@@ -678,18 +678,23 @@ static void plan_bwd_workspace(int64_t B, int64_t N, int64_t C, char* base, Trim
 template <int C>
 static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, const float* p_in, const float* g_in,
                         const float* p_out, const float* g_out, const float* gin, const float* gout, int incoming,
-                        int64_t B, int64_t N, const bf16* out, const bf16* zln, const float* mean_in,
+                        int64_t B, int64_t N, int64_t NN, int stages, bf16* dx_io, bf16* da_io, bf16* db_io,
+                        const bf16* out, const bf16* zln, const float* mean_in,
                         const float* rstd_in, const bf16* a_cm, const bf16* b_cm, const bf16* gate, const bf16* x_cm,
                         const bf16* xln, const float* mean_out, const float* rstd_out, bf16* d_z, float* d_p_in,
                         float* d_g_in, float* d_p_out, float* d_g_out, float* d_gin, float* d_bin, float* d_gout,
                         float* d_bout, char* workspace, int* status, cudaStream_t stream) {
-  const int64_t NN = N * N, R = B * NN;
+  const int64_t R = B * NN;
   TrimulBwdWorkspace w;
-  plan_bwd_workspace(B, N, C, workspace, &w);
+  plan_bwd_workspace(B, NN, C, workspace, &w);
+  if (dx_io) w.dx_cm = dx_io;  // staged (sharded) use: the caller moves these between ranks
+  if (da_io) w.da_cm = da_io;
+  if (db_io) w.db_cm = db_io;
   TrimulPacked pk;
   int rc;
   if ((rc = pack_weights(p_in, g_in, p_out, g_out, w.wpack, C, &pk, stream))) return rc;
 
+  if (stages & 1) {
   // 1. output gate: d_y, d_glogit
   {
     int blocks = (int)((R * C / 8 + 255) / 256);
@@ -731,6 +736,8 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
                                                                        d_bout, C);
     TPF_LAUNCH_OK();
   }
+  }
+  if (stages & 2) {
   // 4. contraction backward
   if (!incoming) {
     // d_a[c,i,k] = sum_j d_x[c,i,j] b[c,j,k] ; d_b[c,j,k] = sum_i d_x[c,i,j] a[c,i,k]
@@ -741,6 +748,8 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     if ((rc = bmm_bf16(b_cm, N, NN, 0, w.dx_cm, N, NN, 0, w.da_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream))) return rc;
     if ((rc = bmm_bf16(a_cm, N, NN, 0, w.dx_cm, N, NN, 1, w.db_cm, N, NN, 0, N, N, N, B * C, 0, 128, stream))) return rc;
   }
+  }
+  if (stages & 4) {
   // 5. gated projections backward (recompute p, g) -> d_proj5[:, 0:4C]
   {
     EpiGateSplitBwd::Params ep{w.da_cm, w.db_cm, mask, w.d_proj5, C, NN};
@@ -777,6 +786,16 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
                                                                        d_bin, C);
     TPF_LAUNCH_OK();
   }
+  }
+  return TPF_OK;
+}
+
+static int check_trimul_rows(const char* who, int64_t N, int64_t NN, int stages) {
+  TPF_REQUIRE(stages >= 1 && stages <= 7, TPF_ERR_INVALID_ARGUMENT, "%s: stages must be a non-empty mask of 1|2|4", who);
+  TPF_REQUIRE(NN > 0 && NN % 64 == 0, TPF_ERR_UNSUPPORTED, "%s: rows per batch (%lld) must be a positive multiple of 64",
+              who, (long long)NN);
+  TPF_REQUIRE(NN == N * N || !(stages & 2), TPF_ERR_INVALID_ARGUMENT,
+              "%s: the contraction stage needs whole pair tensors (rows per batch == N*N)", who);
   return TPF_OK;
 }
 
@@ -792,9 +811,9 @@ static int check_trimul_shape(const char* who, int64_t B, int64_t N, int64_t C) 
 
 int64_t trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C) { return align256(packed_weight_elems(C) * 2); }
 
-int64_t trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C) {
+int64_t trimul_bwd_workspace_bytes(int64_t B, int64_t NN, int64_t C) {
   TrimulBwdWorkspace w;
-  plan_bwd_workspace(B, N, C, nullptr, &w);
+  plan_bwd_workspace(B, NN, C, nullptr, &w);
   return w.total_bytes;
 }
 
@@ -802,9 +821,11 @@ int trimul_fwd(const void* z, const float* mask, const float* p_in, const float*
                const float* g_out, const float* gin, const float* bin, const float* gout, const float* bout,
                int incoming, int64_t B, int64_t N, int64_t C, void* out, void* zln, float* mean_in, float* rstd_in,
                void* a_cm, void* b_cm, void* gate, void* x_cm, void* xln, float* mean_out, float* rstd_out,
-               void* workspace, int64_t workspace_bytes, cudaStream_t stream) {
+               void* workspace, int64_t workspace_bytes, int64_t NN, int stages, cudaStream_t stream) {
   int rc = check_trimul_shape("trimul_fwd", B, N, C);
   if (rc) return rc;
+  if (NN == 0) NN = N * N;
+  if ((rc = check_trimul_rows("trimul_fwd", N, NN, stages))) return rc;
   TPF_REQUIRE(z && mask && p_in && g_in && p_out && g_out && gin && bin && gout && bout && out && zln && mean_in &&
                   rstd_in && a_cm && b_cm && gate && x_cm && xln && mean_out && rstd_out,
               TPF_ERR_INVALID_ARGUMENT, "trimul_fwd: null pointer");
@@ -816,7 +837,7 @@ int trimul_fwd(const void* z, const float* mask, const float* p_in, const float*
   if ((rc = pack_weights(p_in, g_in, p_out, g_out, workspace, (int)C, &pk, stream))) return rc;
 #define TPF_TRIMUL_FWD(CC)                                                                                         \
   if (C == CC)                                                                                                     \
-    return trimul_fwd_t<CC>((const bf16*)z, mask, pk, gin, bin, gout, bout, incoming, B, N, (bf16*)out, (bf16*)zln, \
+    return trimul_fwd_t<CC>((const bf16*)z, mask, pk, gin, bin, gout, bout, incoming, B, N, NN, stages, (bf16*)out, (bf16*)zln, \
                             mean_in, rstd_in, (bf16*)a_cm, (bf16*)b_cm, (bf16*)gate, (bf16*)x_cm, (bf16*)xln,       \
                             mean_out, rstd_out, status, stream);
   TPF_TRIMUL_FWD(32)
@@ -833,23 +854,26 @@ int trimul_bwd(const void* d_out, const void* z, const float* mask, const float*
                const void* a_cm, const void* b_cm, const void* gate, const void* x_cm, const void* xln,
                const float* mean_out, const float* rstd_out, void* d_z, float* d_p_in, float* d_g_in, float* d_p_out,
                float* d_g_out, float* d_gin, float* d_bin, float* d_gout, float* d_bout, void* workspace,
-               int64_t workspace_bytes, cudaStream_t stream) {
+               int64_t workspace_bytes, int64_t NN, int stages, void* dx_io, void* da_io, void* db_io,
+               cudaStream_t stream) {
   int rc = check_trimul_shape("trimul_bwd", B, N, C);
   if (rc) return rc;
+  if (NN == 0) NN = N * N;
+  if ((rc = check_trimul_rows("trimul_bwd", N, NN, stages))) return rc;
   TPF_REQUIRE(d_out && z && mask && p_in && g_in && p_out && g_out && gin && gout && out && zln && mean_in &&
                   rstd_in && a_cm && b_cm && gate && x_cm && xln && mean_out && rstd_out && d_z && d_p_in && d_g_in &&
                   d_p_out && d_g_out && d_gin && d_bin && d_gout && d_bout,
               TPF_ERR_INVALID_ARGUMENT, "trimul_bwd: null pointer");
-  TPF_REQUIRE(workspace && workspace_bytes >= trimul_bwd_workspace_bytes(B, N, C) &&
+  TPF_REQUIRE(workspace && workspace_bytes >= trimul_bwd_workspace_bytes(B, NN, C) &&
                   (reinterpret_cast<uintptr_t>(workspace) & 255) == 0,
               TPF_ERR_WORKSPACE, "trimul_bwd: 256-byte aligned workspace of %lld bytes required",
-              (long long)trimul_bwd_workspace_bytes(B, N, C));
+              (long long)trimul_bwd_workspace_bytes(B, NN, C));
   int* status = nullptr;
   TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_trimul_status));
 #define TPF_TRIMUL_BWD(CC)                                                                                            \
   if (C == CC)                                                                                                        \
     return trimul_bwd_t<CC>((const bf16*)d_out, (const bf16*)z, mask, p_in, g_in, p_out, g_out, gin, gout, incoming,  \
-                            B, N, (const bf16*)out, (const bf16*)zln, mean_in, rstd_in, (const bf16*)a_cm,            \
+                            B, N, NN, stages, (bf16*)dx_io, (bf16*)da_io, (bf16*)db_io, (const bf16*)out, (const bf16*)zln, mean_in, rstd_in, (const bf16*)a_cm,            \
                             (const bf16*)b_cm, (const bf16*)gate, (const bf16*)x_cm, (const bf16*)xln, mean_out,      \
                             rstd_out, (bf16*)d_z, d_p_in, d_g_in, d_p_out, d_g_out, d_gin, d_bin, d_gout, d_bout,     \
                             (char*)workspace, status, stream);
