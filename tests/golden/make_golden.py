@@ -66,10 +66,54 @@ def golden_trimul(ref, path, direction):
         loss=np.float64(loss.item()))
 
 
+def _load_trimul(mod, w, c):
+    with torch.no_grad():
+        mod.layer_norm_in.weight.copy_(w["norm_in_weight"]); mod.layer_norm_in.bias.copy_(w["norm_in_bias"])
+        mod.layer_norm_out.weight.copy_(w["norm_out_weight"]); mod.layer_norm_out.bias.copy_(w["norm_out_bias"])
+        mod.linear_a_p.weight.copy_(w["p_in_weight"][:c]); mod.linear_b_p.weight.copy_(w["p_in_weight"][c:])
+        mod.linear_a_g.weight.copy_(w["g_in_weight"][:c]); mod.linear_b_g.weight.copy_(w["g_in_weight"][c:])
+        mod.linear_z.weight.copy_(w["p_out_weight"]); mod.linear_g.weight.copy_(w["g_out_weight"])
+
+
+def _load_attention(mod, p):
+    with torch.no_grad():
+        mod.layer_norm.weight.copy_(p["ln_w"]); mod.layer_norm.bias.copy_(p["ln_b"])
+        mod.linear_z.weight.copy_(p["w_z"])
+        mod.mha.linear_q.weight.copy_(p["w_q"]); mod.mha.linear_k.weight.copy_(p["w_k"])
+        mod.mha.linear_v.weight.copy_(p["w_v"]); mod.mha.linear_g.weight.copy_(p["w_g"])
+        mod.mha.linear_o.weight.copy_(p["w_o"])
+
+
+def golden_pair_block(ref, path):
+    """TriMul out -> in -> attention start -> end with residuals, composed from the reference's own
+    modules exactly as PairBlock.tri_mul_out_in / tri_att_start_end do (base_blocks.py:311-431)."""
+    from oracle.pair_block_oracle import block_params
+    c, heads, d, n = 32, 4, 8, 24
+    params = block_params(c, heads, d, seed=7)
+    g = torch.Generator().manual_seed(11)
+    z = torch.randn(1, n, n, c, generator=g)
+    mask = torch.ones(1, n, n)
+    mask[:, n - 4:, :] = 0
+    mask[:, :, n - 4:] = 0
+    tmo, tmi = ref["TriangleMultiplicationOutgoing"](c, c), ref["TriangleMultiplicationIncoming"](c, c)
+    tas, tae = ref["TriangleAttention"](c, d, heads), ref["TriangleAttention"](c, d, heads)
+    _load_trimul(tmo, params["tri_mul_out"], c); _load_trimul(tmi, params["tri_mul_in"], c)
+    _load_attention(tas, params["tri_att_start"]); _load_attention(tae, params["tri_att_end"])
+    with torch.no_grad():
+        x = z + tmo(z, mask=mask)
+        x = x + tmi(x, mask=mask)
+        x = x + tas(x, mask=mask)
+        x = x.transpose(-2, -3)
+        x = x + tae(x, mask=mask.transpose(-1, -2), transpose_bias=True)
+        x = x.transpose(-2, -3)
+    np.savez_compressed(path, z=z.numpy(), mask=mask.numpy(), out=x.numpy())
+
+
 if __name__ == "__main__":
     ref = import_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     golden_attention(ref, os.path.join(HERE, "attention_cpu_case.npz"))
     for d in ("outgoing", "incoming"):
         golden_trimul(ref, os.path.join(HERE, f"trimul_{d}_cpu_case.npz"), d)
+    golden_pair_block(ref, os.path.join(HERE, "pair_block_small.npz"))
     print("golden fixtures written to", HERE)

@@ -83,3 +83,19 @@ def test_trimul_oracle_outgoing_matches_reference_fixture(golden_dir):
 
 def test_trimul_oracle_incoming_matches_reference_fixture(golden_dir):
     _trimul_pin(golden_dir, "incoming")
+
+
+def test_pair_block_oracle_matches_reference_modules(golden_dir):
+    """PairBlock composition (TriMul out/in, attention start/end, residuals) built from the
+    reference's own TriangleAttention / TriangleMultiplication modules."""
+    from oracle.pair_block_oracle import block_params, pair_block_forward
+    gold = np.load(os.path.join(golden_dir, "pair_block_small.npz"))
+    params = block_params(32, 4, 8, seed=7)
+    mask = torch.from_numpy(gold["mask"])
+    out = pair_block_forward(torch.from_numpy(gold["z"]), mask, params, heads=4)
+    # Rows whose keys are ALL masked see logits of -1e9 + s: fp32 (the reference) rounds s away and
+    # returns a uniform average, fp64 does not.  Such positions are padding and never feed a valid
+    # position (TriMul multiplies by the mask, attention masks them as keys), so compare valid ones.
+    valid = mask.bool().unsqueeze(-1)
+    ref = torch.from_numpy(gold["out"]).double()
+    _close(torch.where(valid, out, 0.0), torch.where(valid, ref, 0.0), 1e-4, 1e-5)
