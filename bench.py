@@ -365,12 +365,55 @@ def run_gpu(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_block(args, rank, world, local_rank):
+    """Strong-scaling measurement of the whole pair-stack block (TriMul out -> in -> attention start ->
+    end, residuals, fwd+bwd) at --block-n, row-sharded over the ranks (axial parallelism)."""
+    import torch.distributed as dist
+    from openfold3_triangle_kernel_b200 import dap
+    from openfold3_triangle_kernel_b200.pair_block import pair_stack_block
+    from oracle.pair_block_oracle import block_params
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev) if world > 1 else dist.init_process_group(
+        "nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1, device_id=dev)
+    n, c, heads, d = args.block_n, 128, 4, 32
+    g = torch.Generator().manual_seed(4)
+    nl = n // world
+    z = torch.randn(1, nl, n, c, generator=g).bfloat16().to(dev).requires_grad_(True)
+    mask = torch.ones(1, nl, n, device=dev)
+    d_out = torch.randn(1, nl, n, c, generator=g).bfloat16().to(dev)
+    params = {k: {m: t.to(dev).requires_grad_(True) for m, t in v.items()} for k, v in block_params(c, heads, d, 5).items()}
+
+    def step():
+        out = pair_stack_block(z, mask, params, heads, group=dist.group.WORLD)
+        out.backward(d_out)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sec = _time_loop(step, args.steps, lambda: dist.barrier())
+    t = torch.tensor([sec / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    flops = 2 * 3 * (12 * n * n * c * c + 2 * n ** 3 * c) + 2 * 14 * n * heads * n * n * d
+    if rank == 0:
+        print(json.dumps(dict(metric="pair_stack_block_fwd_bwd_tflops", value=flops / float(t) / 1e12, unit="TFLOP/s",
+                              n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=float(t) * 1e3,
+                              higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
+                              config=dict(workload=f"pair-stack block N={n}, C_z=128, H=4, D=32, axially sharded over "
+                                                   f"{world} ranks (operator FLOPs only; wrapper Linears uncounted)"))),
+              flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "block"],
+                    help="hotpath: the N=384 operator benchmark (default); block: sharded pair-stack block")
+    ap.add_argument("--block-n", type=int, default=768)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -380,6 +423,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
+    if args.workload == "block":
+        run_block(args, rank, world, local_rank)
+        return
     run_gpu(args, rank, world, local_rank)
 
 
