@@ -270,8 +270,11 @@ __device__ __forceinline__ float lg2_approx(float x) {
   return y;
 }
 __device__ __forceinline__ float sigmoid_fast(float x) {
-  // 1 / (1 + 2^(-x log2 e))
-  return __fdividef(1.0f, 1.0f + ex2_approx(-1.4426950408889634f * x));
+  // 0.5 tanh(x / 2) + 0.5: one MUFU op (tanh.approx, abs. error ~5e-4, below bf16 resolution of the
+  // gated values) instead of ex2 + rcp
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(t, 0.5f, 0.5f);
 }
 // Packed fp32 pairs (sm_100 executes two fp32 FMAs / adds per instruction) and 3-input max.
 __device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {

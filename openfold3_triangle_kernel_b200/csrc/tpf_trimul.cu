@@ -554,15 +554,45 @@ __global__ void __launch_bounds__(1024) trimul_colsum_fold_kernel(const float* _
 struct WgradDst {
   float* dst[5];
 };
-__global__ void __launch_bounds__(256) trimul_wgrad_fold_kernel(const float* __restrict__ part, int n_splits, int M,
-                                                                int C, WgradDst d) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= M * C) return;
+__global__ void __launch_bounds__(1024) trimul_wgrad_fold_kernel(const float* __restrict__ part, int n_splits, int M,
+                                                                 int C, WgradDst d) {
+  // one CTA per 32 elements: warp w adds splits w, w+32, ... in ascending order, then the 32 warp
+  // sums are added in warp order (a fixed summation tree, no atomics)
+  __shared__ float red[32][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 32 + lane;
   float s = 0.f;
-#pragma unroll 8
-  for (int k = 0; k < n_splits; ++k) s = __fadd_rn(s, part[(int64_t)k * M * C + i]);
-  const int row = i / C, col = i % C;
-  d.dst[row / C][(row % C) * C + col] = s;
+  if (i < M * C)
+    for (int k = warp; k < n_splits; k += 32) s = __fadd_rn(s, part[(int64_t)k * M * C + i]);
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && i < M * C) {
+    float t = red[0][lane];
+#pragma unroll
+    for (int w = 1; w < 32; ++w) t = __fadd_rn(t, red[w][lane]);
+    const int row = i / C, col = i % C;
+    d.dst[row / C][(row % C) * C + col] = t;
+  }
+}
+
+// First level of the LayerNorm-gradient fold: out[s][j] = fixed-order sum of in[s*256 .. s*256+255][j].
+__global__ void __launch_bounds__(1024) trimul_colsum_stage_kernel(const float* __restrict__ in, int n_in, int width,
+                                                                   float* __restrict__ out) {
+  __shared__ float red[32][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x * 32 + lane;
+  const int b0 = blockIdx.y * 256, b1 = min(n_in, b0 + 256);
+  float s = 0.f;
+  if (j < width)
+    for (int b = b0 + warp; b < b1; b += 32) s = __fadd_rn(s, in[(int64_t)b * width + j]);
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && j < width) {
+    float t = red[0][lane];
+#pragma unroll
+    for (int w = 1; w < 32; ++w) t = __fadd_rn(t, red[w][lane]);
+    out[(int64_t)blockIdx.y * width + j] = t;
+  }
 }
 
 // =============================================================================================
@@ -640,7 +670,7 @@ static void split_plan(int64_t R, int tiles_mn, int* n_splits, int64_t* k_per_sp
 
 struct TrimulBwdWorkspace {
   bf16 *wpack, *d_y, *d_proj5, *d_xln, *dx_cm, *da_cm, *db_cm;  // d_zln aliases d_xln
-  float *part_w5, *part_wz, *part_ln_out, *part_ln_in;
+  float *part_w5, *part_wz, *part_ln_out, *part_ln_in, *part_lvl2;
   int splits_w5, splits_wz, blocks_ln_out, blocks_ln_in, rows_per_block_in;
   int64_t kps_w5, kps_wz;
   int64_t total_bytes;
@@ -672,6 +702,10 @@ static void plan_bwd_workspace(int64_t B, int64_t NN, int64_t C, char* base, Tri
   w->blocks_ln_in = (int)((R + 255) / 256);
   w->part_ln_out = reinterpret_cast<float*>(take((int64_t)w->blocks_ln_out * 2 * C * 4));
   w->part_ln_in = reinterpret_cast<float*>(take((int64_t)w->blocks_ln_in * 2 * C * 4));
+  {
+    const int64_t most = w->blocks_ln_out > w->blocks_ln_in ? w->blocks_ln_out : w->blocks_ln_in;
+    w->part_lvl2 = reinterpret_cast<float*>(take(((most + 255) / 256) * 2 * C * 4));
+  }
   w->total_bytes = off;
 }
 
@@ -716,7 +750,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
   {
     WgradDst d;
     for (int i = 0; i < 5; ++i) d.dst[i] = d_p_out;
-    trimul_wgrad_fold_kernel<<<(C * C + 255) / 256, 256, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
+    trimul_wgrad_fold_kernel<<<(C * C + 31) / 32, 1024, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
     TPF_LAUNCH_OK();
   }
   // 3. output norm backward -> d_x (channel-major), d_gamma_out, d_beta_out
@@ -732,9 +766,14 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     kern<<<(unsigned)(B * tiles), 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out,
                                                        NN, tiles);
     TPF_LAUNCH_OK();
-    trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(w.part_ln_out, w.blocks_ln_out, 2 * C, d_gout,
-                                                                       d_bout, C);
-    TPF_LAUNCH_OK();
+    {
+      const int lvl = (w.blocks_ln_out + 255) / 256;
+      trimul_colsum_stage_kernel<<<dim3((2 * C + 31) / 32, lvl), 1024, 0, stream>>>(w.part_ln_out, w.blocks_ln_out,
+                                                                                    2 * C, w.part_lvl2);
+      TPF_LAUNCH_OK();
+      trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(w.part_lvl2, lvl, 2 * C, d_gout, d_bout, C);
+      TPF_LAUNCH_OK();
+    }
   }
   }
   if (stages & 2) {
@@ -774,7 +813,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     d.dst[2] = d_p_in + C * C;      // b_p
     d.dst[3] = d_g_in + C * C;      // b_g
     d.dst[4] = d_g_out;             // g
-    trimul_wgrad_fold_kernel<<<(5 * C * C + 255) / 256, 256, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
+    trimul_wgrad_fold_kernel<<<(5 * C * C + 31) / 32, 1024, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
     TPF_LAUNCH_OK();
   }
   // 7. input norm backward
@@ -782,9 +821,14 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     trimul_ln_bwd_kernel<C><<<w.blocks_ln_in, 256, 0, stream>>>(d_zln, z, gin, mean_in, rstd_in, d_z, w.part_ln_in, R,
                                                                 w.rows_per_block_in);
     TPF_LAUNCH_OK();
-    trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(w.part_ln_in, w.blocks_ln_in, 2 * C, d_gin,
-                                                                       d_bin, C);
-    TPF_LAUNCH_OK();
+    {
+      const int lvl = (w.blocks_ln_in + 255) / 256;
+      trimul_colsum_stage_kernel<<<dim3((2 * C + 31) / 32, lvl), 1024, 0, stream>>>(w.part_ln_in, w.blocks_ln_in,
+                                                                                    2 * C, w.part_lvl2);
+      TPF_LAUNCH_OK();
+      trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(w.part_lvl2, lvl, 2 * C, d_gin, d_bin, C);
+      TPF_LAUNCH_OK();
+    }
   }
   }
   return TPF_OK;
