@@ -20,6 +20,8 @@
 //    S and dP (two cheap K = D GEMMs) and summing dS in fp32 registers in ascending o.
 //    A few independent o-chunks per tile fill the machine; their partial planes are folded
 //    in fixed order by a tiny kernel.
+#include <stdlib.h>
+
 #include "tpf_host.cuh"
 #include "tpf_ptx.cuh"
 
@@ -437,23 +439,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     };
 
+    // lse / delta of this thread's query row, loaded one query tile ahead of their first use
+    float l_pref = -INFINITY, d_pref = 0.f;
+    auto prefetch_row_scalars = [&](const BwdWalk& t) {
+      l_pref = -INFINITY;
+      d_pref = 0.f;
+      if (t.valid()) {
+        int pb, po, phh;
+        decode(t.item, pb, po, phh);
+        const int pq = t.qt * 128 + row;
+        if (pq < p.N) {
+          const int64_t idx = (((int64_t)pb * p.O + po) * p.H + phh) * p.N + pq;
+          l_pref = p.lse[idx];
+          d_pref = p.delta[idx];
+        }
+      }
+    };
+
     BwdWalk w;
     w.init(blockIdx.x, gridDim.x, p.n_items, p.q_tiles, p.k_tiles, KS, p.n_strips);
+    prefetch_row_scalars(w);
     for (; w.valid(); w.next()) {
       int b, o, h;
       decode(w.item, b, o, h);
       const int q = w.qt * 128 + row;
       const int kt = w.kt();
       if (w.first_kk()) {
-        if (q < p.N) {
-          const int64_t idx = (((int64_t)b * p.O + o) * p.H + h) * p.N + q;
-          const float l = p.lse[idx];
-          neg_lse2 = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
-          delta = p.delta[idx];
-        } else {
-          neg_lse2 = -INFINITY;
-          delta = 0.f;
-        }
+        // values fetched one query tile ahead; fetch the next tile's now
+        neg_lse2 = (l_pref == -INFINITY) ? -INFINITY : -l_pref * kLog2e;
+        delta = d_pref;
+        BwdWalk nx = w;
+        const int sl = w.strip_len();
+        for (int t = 0; t < sl; ++t) nx.next();
+        prefetch_row_scalars(nx);
       }
 
       // ---------------- phase 1: P = exp(S - lse)
@@ -654,13 +672,17 @@ struct AttnDbiasCfg {
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
-template <class Cfg>
-__global__ void __launch_bounds__(320, 1)
+// NCW compute warps: NCW / 4 threads share one query row (TMEM lane) and split the 128 keys of the tile.
+template <class Cfg, int NCW>
+__global__ void __launch_bounds__(NCW == 8 ? 320 : 640, 1)
 attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                   const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
                   const AttnDbiasParams p, int* __restrict__ status) {
   constexpr int D = Cfg::D, NST = Cfg::NST;
+  constexpr int WARP_TMA = NCW, WARP_MMA = NCW + 1;
+  constexpr int CPT = 128 / (NCW / 4);      // key columns per thread
+  constexpr int SUB = NCW == 8 ? 32 : 16;   // columns per TMEM load
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
@@ -689,11 +711,11 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 9);
+      mbar_init(&empty[s], 1 + NCW);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sdp_full[s], 1);
-      mbar_init(&sdp_free[s], 8);
+      mbar_init(&sdp_free[s], NCW);
     }
     mbar_init(bias_full, 1);
     *abort_flag = 0;
@@ -705,7 +727,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tma_prefetch_desc(&tmBias);
     tma_prefetch_desc(&tmMask);
   }
-  if (warp == 9) {
+  if (warp == WARP_MMA) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -714,7 +736,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == WARP_TMA) {
     if (lane == 0) {
       mbar_expect_tx(bias_full, 32768);
       tma_load_4d(smem + Cfg::OFF_BIAS, &tmBias, bias_full, kt * 128, qt * 128, h, g);
@@ -737,7 +759,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == WARP_MMA) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t swz = swizzle_mode_for_bytes(Cfg::SWZ);
@@ -766,8 +788,8 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
     }
-  } else {
-    const int hf = warp >> 2;
+  } else if (warp < NCW) {
+    const int part = warp >> 2;               // which CPT-column slice of the tile
     const int row = 32 * (warp & 3) + lane;
     const uint32_t lane_base = 32 * (warp & 3);
     constexpr float kLog2e = 1.4426950408889634f;
@@ -775,55 +797,66 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int q = qt * 128 + row;
     const bool tail = (kt + 1) * 128 > p.N;
 
-    float acc[64];
+    float acc[CPT];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+    for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
 
     mbar_wait(bias_full, 0, wctx);  // the bias tile of this CTA stays in shared memory
 
-    auto load_row_scalars = [&](int pl, float& nl2, float& dl) {
-      nl2 = -INFINITY;
+    // lse / delta of (plane, h, q): planes of one group are consecutive in memory, so the index
+    // advances by H * N per step (no division in the loop)
+    const int64_t row_stride = (int64_t)p.H * p.N;
+    const int64_t row_idx0 = ((int64_t)g * b_per_g * p.O * p.H + h) * p.N + q;
+    // raw loads only: the values are first touched one step later, so the load latency is off the
+    // critical path
+    auto load_row_scalars = [&](int pl, float& l, float& dl) {
+      l = -INFINITY;
       dl = 0.f;
       if (pl < pl1 && q < p.N) {
-        const int b = g * b_per_g + pl / p.O, o = pl % p.O;
-        const int64_t idx = (((int64_t)b * p.O + o) * p.H + h) * p.N + q;
-        const float l = p.lse[idx];
-        nl2 = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
+        const int64_t idx = row_idx0 + (int64_t)pl * row_stride;
+        l = p.lse[idx];
         dl = p.delta[idx];
       }
     };
 
     int s = 0, buf = 0;
     uint32_t ph = 0, full_ph[2] = {0, 0};
-    float nl2_next, dl_next;
-    load_row_scalars(pl0, nl2_next, dl_next);
+    float l_next, dl_next;
+    load_row_scalars(pl0, l_next, dl_next);
     for (int pl = pl0; pl < pl1; ++pl) {
-      const float neg_lse2 = nl2_next, delta = dl_next;
-      load_row_scalars(pl + 1, nl2_next, dl_next);
+      const float neg_lse2 = (l_next == -INFINITY) ? -INFINITY : -l_next * kLog2e, delta = dl_next;
+      load_row_scalars(pl + 1, l_next, dl_next);
       mbar_wait(&sdp_full[buf], full_ph[buf], wctx);
       full_ph[buf] ^= 1;
       mbar_wait(&full[s], ph, wctx);
       tc_fence_after();
-      const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_ST + s * Cfg::STAGE + 4 * Cfg::TILE) + 64 * hf;
-      const uint32_t t_s = tmem_addr(tmem_base, lane_base, buf * 256 + 64 * hf);
-      const uint32_t t_dp = tmem_addr(tmem_base, lane_base, buf * 256 + 128 + 64 * hf);
-      const uint8_t* brow = smem + Cfg::OFF_BIAS + hf * 16384 + row * 128;
+      const float* mask_row =
+          reinterpret_cast<const float*>(smem + Cfg::OFF_ST + s * Cfg::STAGE + 4 * Cfg::TILE) + CPT * part;
+      const uint32_t t_s = tmem_addr(tmem_base, lane_base, buf * 256 + CPT * part);
+      const uint32_t t_dp = tmem_addr(tmem_base, lane_base, buf * 256 + 128 + CPT * part);
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {  // 32 columns per half: two TMEM loads in flight, one wait
-        const int base = 32 * hh;
-        uint32_t rs[32], rd[32];
-        tmem_ld32(t_s + base, rs);
-        tmem_ld32(t_dp + base, rd);
+      for (int hh = 0; hh < CPT / SUB; ++hh) {  // SUB columns per step: two TMEM loads in flight, one wait
+        const int base = SUB * hh;
+        uint32_t rs[SUB], rd[SUB];
+        if constexpr (SUB == 32) {
+          tmem_ld32(t_s + base, rs);
+          tmem_ld32(t_dp + base, rd);
+        } else {
+          tmem_ld16(t_s + base, rs);
+          tmem_ld16(t_dp + base, rd);
+        }
         tmem_ld_wait();
-        if (hh == 1) {
+        if (hh == CPT / SUB - 1) {
           // the whole TMEM tile is in registers: the next S / dP pair may overwrite it
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sdp_free[buf]);
         }
+        const int col0 = CPT * part + base;  // first column of this step inside the 128-key tile
+        const uint8_t* brow = smem + Cfg::OFF_BIAS + (col0 >> 6) * 16384 + row * 128;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {  // 8 columns per step
-          const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((4 * hh + u) ^ (row & 7)) << 4));
+        for (int u = 0; u < SUB / 8; ++u) {  // 8 columns per step
+          const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((((col0 & 63) >> 3) + u) ^ (row & 7)) << 4));
           const uint32_t bw4[4] = {bv.x, bv.y, bv.z, bv.w};
           const float4 mk0 = *reinterpret_cast<const float4*>(mask_row + base + 8 * u);
           const float4 mk1 = *reinterpret_cast<const float4*>(mask_row + base + 8 * u + 4);
@@ -835,8 +868,8 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             float v0 = fmaf(__uint_as_float(rs[i0]), scale, __uint_as_float(bw << 16)) + mk[2 * e];
             float v1 = fmaf(__uint_as_float(rs[i0 + 1]), scale, __uint_as_float(bw & 0xFFFF0000u)) + mk[2 * e + 1];
             if (tail) {
-              if (kt * 128 + 64 * hf + base + i0 >= p.N) v0 = -INFINITY;
-              if (kt * 128 + 64 * hf + base + i0 + 1 >= p.N) v1 = -INFINITY;
+              if (kt * 128 + col0 + i0 >= p.N) v0 = -INFINITY;
+              if (kt * 128 + col0 + i0 + 1 >= p.N) v1 = -INFINITY;
             }
             const float p0 = ex2_approx(fmaf(v0, kLog2e, neg_lse2));
             const float p1 = ex2_approx(fmaf(v1, kLog2e, neg_lse2));
@@ -855,15 +888,15 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
 
     if (q < p.N) {
-      const int k0 = kt * 128 + 64 * hf;
+      const int k0 = kt * 128 + CPT * part;
       float* dst = p.part + ((((int64_t)chunk * p.G + g) * p.H + h) * p.N + q) * p.N + k0;
-      if ((p.N & 3) == 0 && k0 + 64 <= p.N) {
+      if ((p.N & 3) == 0 && k0 + CPT <= p.N) {
 #pragma unroll
-        for (int i = 0; i < 64; i += 4)
+        for (int i = 0; i < CPT; i += 4)
           *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < CPT; ++i)
           if (k0 + i < p.N) dst[i] = acc[i];
       }
     }
@@ -871,7 +904,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == WARP_MMA) {
     __syncwarp();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
@@ -998,13 +1031,17 @@ int launch_attn_dbias(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
                       const CUtensorMap& tb, const CUtensorMap& tmk, AttnDbiasParams& p, int* status, int grid,
                       cudaStream_t stream) {
   using Cfg = AttnDbiasCfg<D>;
-  auto kern = attn_dbias_kernel<Cfg>;
+  constexpr bool wide = true;  // 16 compute warps: measured 159 us vs 204 us with 8 at B=1, O=N=384, H=4, D=32
   static bool attr_done = false;
   if (!attr_done) {
-    TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    TPF_CUDA_OK(cudaFuncSetAttribute(attn_dbias_kernel<Cfg, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::SMEM_BYTES));
+    TPF_CUDA_OK(cudaFuncSetAttribute(attn_dbias_kernel<Cfg, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::SMEM_BYTES));
     attr_done = true;
   }
-  kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
+  if (wide) attn_dbias_kernel<Cfg, 16><<<grid, 640, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
+  else attn_dbias_kernel<Cfg, 8><<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }
