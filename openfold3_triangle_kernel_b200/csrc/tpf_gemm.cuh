@@ -5,7 +5,8 @@
 // One CTA per SM walks a static list of (batch, m-tile, n-tile) output tiles.
 //   warp 0      : TMA producer  (one elected lane) - STAGES-deep smem ring
 //   warp 1      : UMMA issuer   (one elected lane) - accumulators double-buffered in TMEM
-//   warps 2..9  : epilogue      (two warps per 32 TMEM lanes = rows; alternate 32-column chunks)
+//   warps 2..   : epilogue      (8 or 16 warps: two or four per 32 TMEM lanes = rows; they
+//                               interleave 32-column chunks)
 // Either operand may be K-major (k contiguous in memory) or MN-major (m / n
 // contiguous); the shared-memory tiles are written by TMA in the swizzled
 // canonical layouts the UMMA descriptors describe, so no thread touches them.
@@ -24,10 +25,13 @@ struct GemmShape {
                     // k in [b*k_per_split, (b+1)*k_per_split) of ONE problem
 };
 
-template <int BM_, int BN_, int SWZ_A_, bool A_MN_, int SWZ_B_, bool B_MN_, int STAGES_>
+template <int BM_, int BN_, int SWZ_A_, bool A_MN_, int SWZ_B_, bool B_MN_, int STAGES_, int EPI_WARPS_ = 8>
 struct GemmCfg {
   static constexpr int BM = BM_, BN = BN_, SWZ_A = SWZ_A_, SWZ_B = SWZ_B_, STAGES = STAGES_;
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_;
+  static constexpr int EPI_WARPS = EPI_WARPS_;          // 8 or 16: warps per TMEM lane quarter x 4
+  static constexpr int EPI_PER_Q = EPI_WARPS / 4;       // warps sharing one lane quarter; they interleave 32-column chunks
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int BK_A = A_MN ? 64 : SWZ_A / 2;
   static constexpr int BK_B = B_MN ? 64 : SWZ_B / 2;
   static constexpr int BK = BK_A < BK_B ? BK_A : BK_B;  // k elements per pipeline stage
@@ -38,6 +42,7 @@ struct GemmCfg {
   static constexpr int ACC_STRIDE = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;  // TMEM columns per accumulator
   static constexpr int TMEM_COLS = 2 * ACC_STRIDE;  // two accumulators; power of two >= 32
   static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 256 + 1024;
+  static_assert(EPI_WARPS == 8 || EPI_WARPS == 16, "epilogue warps");
   static_assert(BM == 128, "UMMA tile M is 128 (one TMEM lane per row)");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
   static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
@@ -45,6 +50,37 @@ struct GemmCfg {
   static_assert(BN % 32 == 0, "the epilogue walks 32 accumulator columns at a time");
   static_assert(A_BYTES % 1024 == 0 && B_BYTES % 1024 == 0, "stage buffers keep 1024-byte alignment");
 };
+
+// ---- per-warp staging of a 32 x 32 bf16 block --------------------------------------------------
+// In the epilogue lane = accumulator row, so a lane holds 32 consecutive columns (64 bytes) of its
+// row.  Stored straight from the registers, one 16-byte store instruction touches 32 different
+// rows: 32 memory transactions that each fill half a sector.  Staged through a 2 KiB per-warp
+// shared-memory tile (16-byte pieces XOR-swizzled so that both phases are bank-conflict free),
+// every store instruction covers 8 rows x 64 contiguous bytes.
+__device__ __forceinline__ void warp_tile_put(uint8_t* tile, int lane, const uint32_t (&pk)[16]) {
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(tile + lane * 64 + ((i ^ sw) << 4)) =
+        make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+}
+__device__ __forceinline__ uint4 warp_tile_get(const uint8_t* tile, int row, int piece) {
+  return *reinterpret_cast<const uint4*>(tile + row * 64 + ((piece ^ ((row >> 1) & 3)) << 4));
+}
+// row_ptr(r) -> address of the first of row r's 32 columns (16-byte aligned), or nullptr to skip the row.
+// All 32 lanes must call this together.
+template <class RowPtr>
+__device__ __forceinline__ void warp_tile_store(uint8_t* tile, int lane, const uint32_t (&pk)[16], RowPtr row_ptr) {
+  warp_tile_put(tile, lane, pk);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 8 * i + (lane >> 2), piece = lane & 3;
+    __nv_bfloat16* dst = row_ptr(r);
+    if (dst != nullptr) *reinterpret_cast<uint4*>(dst + 8 * piece) = warp_tile_get(tile, r, piece);
+  }
+  __syncwarp();
+}
 
 // Plain stores.  OutT = __nv_bfloat16 or float; row-major D[b][m][n] with leading dimension ldd.
 template <typename OutT>
@@ -55,27 +91,33 @@ struct EpiStore {
     int64_t batch_stride;
   };
   static constexpr bool kPaired = false;
-  static constexpr int kSmemPerWarp = 0;  // bytes of per-warp epilogue scratch
+  static constexpr int kSmemPerWarp = sizeof(OutT) == 2 ? 2048 : 0;  // bytes of per-warp epilogue scratch
+  // Global-memory operands of the epilogue, requested before the accumulator wait so that their
+  // latency hides behind the UMMAs instead of stalling the (few) epilogue warps chunk by chunk.
+  struct Pre {};
+  __device__ static __forceinline__ void prefetch(const Params&, const GemmShape&, int, int, int, int, Pre&) {}
   __device__ static __forceinline__ void apply(const Params& p, const GemmShape& sh, int b, int m, int n0,
-                                               const float (&v)[32], float*, int) {
-    if (m >= sh.M) return;
-    OutT* row = p.D + (int64_t)b * p.batch_stride + (int64_t)m * p.ldd + n0;
-    if (n0 + 32 <= sh.N && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
-      if constexpr (sizeof(OutT) == 2) {
+                                               const float (&v)[32], float* wsm, int lane, const Pre&) {
+    OutT* blk = p.D + (int64_t)b * p.batch_stride + n0;  // column n0 of row 0
+    if constexpr (sizeof(OutT) == 2) {
+      // warp-uniform test: whole 32-column block inside N and every row 16-byte aligned
+      if (n0 + 32 <= sh.N && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(blk) & 15) == 0) {
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 u;
-          u.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-          u.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-          u.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-          u.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-          reinterpret_cast<uint4*>(row)[i] = u;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          reinterpret_cast<float4*>(row)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+        const int m_base = m - lane;
+        warp_tile_store(reinterpret_cast<uint8_t*>(wsm), lane, pk, [&](int r) -> __nv_bfloat16* {
+          return m_base + r < sh.M ? blk + (int64_t)(m_base + r) * p.ldd : nullptr;
+        });
+        return;
       }
+    }
+    if (m >= sh.M) return;
+    OutT* row = blk + (int64_t)m * p.ldd;
+    if (sizeof(OutT) == 4 && n0 + 32 <= sh.N && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(row)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i)
@@ -85,7 +127,7 @@ struct EpiStore {
 };
 
 template <class Cfg, class Epi>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmShape sh, const typename Epi::Params ep, int* __restrict__ status) {
   extern __shared__ uint8_t smem_dyn[];
@@ -118,7 +160,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 8);
+      mbar_init(&tempty[a], Cfg::EPI_WARPS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -214,7 +256,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // 8 epilogue warps: two per TMEM lane quarter; they take alternate 32-column chunks
+    // epilogue warps: EPI_PER_Q per TMEM lane quarter; they interleave 32-column chunks
     const int lane_base = 32 * (warp & 3);
     const int chunk_par = (warp - 2) >> 2;
     float* wsm = reinterpret_cast<float*>(epi_smem + (warp - 2) * Epi::kSmemPerWarp);
@@ -225,17 +267,23 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int r = t - b * (mt * nt);
       const int m0 = (r / nt) * Cfg::BM;
       const int n0 = (r % nt) * Cfg::BN;
-      mbar_wait(&tfull[acc], acc_ph, wctx);
-      tc_fence_after();
       const uint32_t t_acc = tmem_addr(tmem_base, lane_base, acc * Cfg::ACC_STRIDE);
       const int m = m0 + lane_base + lane;
       if constexpr (!Epi::kPaired) {
         // all of this warp's 32-column chunks are requested before the single wait
-        constexpr int NCH = (Cfg::BN / 32 + 1) / 2;
+        constexpr int NCH = (Cfg::BN / 32 + Cfg::EPI_PER_Q - 1) / Cfg::EPI_PER_Q;
+        typename Epi::Pre pre[NCH];
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+          const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
+          if (c < Cfg::BN && n0 + c < sh.N) Epi::prefetch(ep, sh, b, m, n0 + c, lane, pre[k]);
+        }
+        mbar_wait(&tfull[acc], acc_ph, wctx);
+        tc_fence_after();
         uint32_t raw[NCH][32];
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
-          const int c = 32 * chunk_par + 64 * k;
+          const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
           if (c < Cfg::BN) tmem_ld32(t_acc + c, raw[k]);
         }
         tmem_ld_wait();
@@ -245,21 +293,29 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) mbar_arrive(&tempty[acc]);
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
-          const int c = 32 * chunk_par + 64 * k;
+          const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
           if (c < Cfg::BN && n0 + c < sh.N) {
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[k][i]);
-            Epi::apply(ep, sh, b, m, n0 + c, v, wsm, lane);
+            Epi::apply(ep, sh, b, m, n0 + c, v, wsm, lane, pre[k]);
           }
         }
       } else {
         // Column c (first half of the tile) pairs with column c + BN/2.
-        constexpr int NCH = (Cfg::BN / 64 + 1) / 2;
+        constexpr int NCH = (Cfg::BN / 64 + Cfg::EPI_PER_Q - 1) / Cfg::EPI_PER_Q;
+        typename Epi::Pre pre[NCH];
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+          const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
+          if (c < Cfg::BN / 2) Epi::prefetch2(ep, sh, b, m, n0, c, lane, pre[k]);
+        }
+        mbar_wait(&tfull[acc], acc_ph, wctx);
+        tc_fence_after();
         uint32_t raw0[NCH][32], raw1[NCH][32];
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
-          const int c = 32 * chunk_par + 64 * k;
+          const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
           if (c < Cfg::BN / 2) {
             tmem_ld32(t_acc + c, raw0[k]);
             tmem_ld32(t_acc + Cfg::BN / 2 + c, raw1[k]);
@@ -272,7 +328,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) mbar_arrive(&tempty[acc]);
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
-          const int c = 32 * chunk_par + 64 * k;
+          const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
           if (c < Cfg::BN / 2) {
             float v0[32], v1[32];
 #pragma unroll
@@ -280,7 +336,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               v0[i] = __uint_as_float(raw0[k][i]);
               v1[i] = __uint_as_float(raw1[k][i]);
             }
-            Epi::apply2(ep, sh, b, m, n0, c, v0, v1, wsm, lane);
+            Epi::apply2(ep, sh, b, m, n0, c, v0, v1, wsm, lane, pre[k]);
           }
         }
       }

@@ -33,7 +33,7 @@ int launch_gemm(const void* A, int64_t lda, int64_t bsa, const void* B, int64_t 
   rc = make_operand_tmap(&tmB, B, Cfg::B_MN, sh.N, sh.K, ldb, tensor_batch, bsb, Cfg::SWZ_B, Cfg::BN, Cfg::BK);
   if (rc) return rc;
   auto kern = gemm_umma_kernel<Cfg, Epi>;
-  constexpr int smem_bytes = Cfg::SMEM_BYTES + 8 * Epi::kSmemPerWarp;
+  constexpr int smem_bytes = Cfg::SMEM_BYTES + Cfg::EPI_WARPS * Epi::kSmemPerWarp;
   static_assert(smem_bytes <= 232448, "shared memory budget");
   static bool attr_done = false;  // per instantiation
   if (!attr_done) {
@@ -46,7 +46,7 @@ int launch_gemm(const void* A, int64_t lda, int64_t bsa, const void* B, int64_t 
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid > tiles) grid = tiles;
   if (grid < 1) return TPF_OK;
-  kern<<<grid, 320, smem_bytes, stream>>>(tmA, tmB, sh, ep, status);
+  kern<<<grid, Cfg::THREADS, smem_bytes, stream>>>(tmA, tmB, sh, ep, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }

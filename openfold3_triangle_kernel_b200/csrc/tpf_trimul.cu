@@ -205,38 +205,47 @@ struct EpiProjGate {
   };
   static constexpr bool kPaired = true;
   static constexpr int kSmemPerWarp = 32 * 33 * 4;
+  struct Pre {
+    float mk;  // pair mask of this lane's row
+  };
+  __device__ static __forceinline__ void prefetch2(const Params& p, const GemmShape& sh, int, int m, int, int, int,
+                                                   Pre& pre) {
+    pre.mk = (m < sh.M) ? p.mask[m] : 0.f;
+  }
   __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
-                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane) {
+                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane,
+                                                const Pre& pre) {
     const int which = n0 / (2 * p.C);
+    const int m_base = m - lane;  // first row of this warp's 32-row block (a multiple of 32)
     if (which == 2) {
-      if (m >= sh.M) return;
-      bf16* row = p.gate + (int64_t)m * p.C + c0;
+      uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint4 u;
-        u.x = pack_bf16x2(v0[8 * i + 0], v0[8 * i + 1]);
-        u.y = pack_bf16x2(v0[8 * i + 2], v0[8 * i + 3]);
-        u.z = pack_bf16x2(v0[8 * i + 4], v0[8 * i + 5]);
-        u.w = pack_bf16x2(v0[8 * i + 6], v0[8 * i + 7]);
-        reinterpret_cast<uint4*>(row)[i] = u;
-      }
+      for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(v0[2 * i], v0[2 * i + 1]);
+      bf16* blk = p.gate + c0;
+      warp_tile_store(reinterpret_cast<uint8_t*>(wsm), lane, pk, [&](int r) -> bf16* {
+        return m_base + r < sh.M ? blk + (int64_t)(m_base + r) * p.C : nullptr;
+      });
       return;
     }
-    const float mk = (m < sh.M) ? p.mask[m] : 0.f;
+    const float mk = pre.mk;
 #pragma unroll
     for (int i = 0; i < 32; ++i) wsm[lane * 33 + i] = v0[i] * sigmoid_fast(v1[i]) * mk;
     __syncwarp();
-    const int m_base = m - lane;  // first row of this warp's 32-row block (a multiple of 32)
+    // four lanes per channel: each store instruction covers 8 channels x 64 contiguous bytes (32 rows)
     const int64_t bb = m_base / p.NN, rr = m_base - bb * p.NN;
-    bf16* dst = (which == 0 ? p.a_cm : p.b_cm) + (bb * p.C + c0 + lane) * p.NN + rr;  // lane = channel
+    const int piece = lane & 3;  // rows 8*piece .. 8*piece+7 of the block
+    bf16* dst = (which == 0 ? p.a_cm : p.b_cm) + (bb * p.C + c0 + (lane >> 2)) * p.NN + rr + 8 * piece;
+    const float* col = wsm + (8 * piece) * 33 + (lane >> 2);
+    const bool ok = m_base + 8 * piece + 7 < sh.M;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
+      const float* cg = col + 8 * g;  // channel 8*g + lane/4
       uint4 u;
-      u.x = pack_bf16x2(wsm[(8 * g + 0) * 33 + lane], wsm[(8 * g + 1) * 33 + lane]);
-      u.y = pack_bf16x2(wsm[(8 * g + 2) * 33 + lane], wsm[(8 * g + 3) * 33 + lane]);
-      u.z = pack_bf16x2(wsm[(8 * g + 4) * 33 + lane], wsm[(8 * g + 5) * 33 + lane]);
-      u.w = pack_bf16x2(wsm[(8 * g + 6) * 33 + lane], wsm[(8 * g + 7) * 33 + lane]);
-      if (m_base + 8 * g + 7 < sh.M) *reinterpret_cast<uint4*>(dst + 8 * g) = u;
+      u.x = pack_bf16x2(cg[0 * 33], cg[1 * 33]);
+      u.y = pack_bf16x2(cg[2 * 33], cg[3 * 33]);
+      u.z = pack_bf16x2(cg[4 * 33], cg[5 * 33]);
+      u.w = pack_bf16x2(cg[6 * 33], cg[7 * 33]);
+      if (ok) *reinterpret_cast<uint4*>(dst + (int64_t)(8 * g) * p.NN) = u;
     }
     __syncwarp();
   }
@@ -250,23 +259,34 @@ struct EpiOutGate {
     int C;
   };
   static constexpr bool kPaired = false;
-  static constexpr int kSmemPerWarp = 0;
-  __device__ static __forceinline__ void apply(const Params& p, const GemmShape& sh, int, int m, int n0,
-                                               const float (&v)[32], float*, int) {
+  static constexpr int kSmemPerWarp = 2048;
+  struct Pre {
+    uint4 g[4];  // 32 gate logits of this lane's row
+  };
+  __device__ static __forceinline__ void prefetch(const Params& p, const GemmShape& sh, int, int m, int n0, int,
+                                                  Pre& pre) {
     if (m >= sh.M) return;
-    const bf16* g = p.gate + (int64_t)m * p.C + n0;
-    bf16* o = p.out + (int64_t)m * p.C + n0;
+    const uint4* g = reinterpret_cast<const uint4*>(p.gate + (int64_t)m * p.C + n0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pre.g[i] = g[i];
+  }
+  __device__ static __forceinline__ void apply(const Params& p, const GemmShape& sh, int, int m, int n0,
+                                               const float (&v)[32], float* wsm, int lane, const Pre& pre) {
+    uint32_t ow[16];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 gu = reinterpret_cast<const uint4*>(g)[i];
+      const uint4 gu = m < sh.M ? pre.g[i] : make_uint4(0u, 0u, 0u, 0u);
       const uint32_t gw[4] = {gu.x, gu.y, gu.z, gu.w};
-      uint32_t ow[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        ow[e] = pack_bf16x2(v[8 * i + 2 * e] * sigmoid_fast(bf16_lo(gw[e])),
-                            v[8 * i + 2 * e + 1] * sigmoid_fast(bf16_hi(gw[e])));
-      reinterpret_cast<uint4*>(o)[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        ow[4 * i + e] = pack_bf16x2(v[8 * i + 2 * e] * sigmoid_fast(bf16_lo(gw[e])),
+                                    v[8 * i + 2 * e + 1] * sigmoid_fast(bf16_hi(gw[e])));
     }
+    const int m_base = m - lane;
+    bf16* blk = p.out + n0;
+    warp_tile_store(reinterpret_cast<uint8_t*>(wsm), lane, ow, [&](int r) -> bf16* {
+      return m_base + r < sh.M ? blk + (int64_t)(m_base + r) * p.C : nullptr;
+    });
   }
 };
 
@@ -282,27 +302,46 @@ struct EpiGateSplitBwd {
   };
   static constexpr bool kPaired = true;
   static constexpr int kSmemPerWarp = 32 * 33 * 4;
-  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
-                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane) {
+  struct Pre {
+    uint4 d[4];  // incoming gradient, channel-major: d[g] = 8 consecutive rows of channel 8*g + lane/4
+    float mk;    // pair mask of this lane's row
+  };
+  __device__ static __forceinline__ void prefetch2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
+                                                   int lane, Pre& pre) {
     const int which = n0 / (2 * p.C);  // 0: a, 1: b
-    // incoming gradient block, channel-major: lane = channel reads 32 consecutive rows (4 x 16 bytes),
-    // transposed through smem so that afterwards lane = row holds its 32 channels
     const int m_base = m - lane;
     const int64_t bb = m_base / p.NN, rr = m_base - bb * p.NN;
-    const bf16* src = (which == 0 ? p.da_cm : p.db_cm) + (bb * p.C + c0 + lane) * p.NN + rr;
+    // four lanes per channel: load g reads rows 8*piece..+7 of channel 8*g + lane/4, so one load
+    // instruction covers 8 channels x 64 contiguous bytes
+    const int piece = lane & 3;
+    const bf16* src = (which == 0 ? p.da_cm : p.db_cm) + (bb * p.C + c0 + (lane >> 2)) * p.NN + rr + 8 * piece;
+    const bool ok = m_base + 8 * piece + 7 < sh.M;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      uint4 u = make_uint4(0u, 0u, 0u, 0u);
-      if (m_base + 8 * g + 7 < sh.M) u = *reinterpret_cast<const uint4*>(src + 8 * g);
+      pre.d[g] = make_uint4(0u, 0u, 0u, 0u);
+      if (ok) pre.d[g] = *reinterpret_cast<const uint4*>(src + (int64_t)(8 * g) * p.NN);
+    }
+    pre.mk = (m < sh.M) ? p.mask[m] : 0.f;
+  }
+  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
+                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane,
+                                                const Pre& pre) {
+    const int which = n0 / (2 * p.C);  // 0: a, 1: b
+    // the prefetched channel-major block is transposed through smem so that afterwards lane = row
+    // holds its 32 channels
+    float* col = wsm + (8 * (lane & 3)) * 33 + (lane >> 2);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint4 u = pre.d[g];
       const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        wsm[(8 * g + 2 * e) * 33 + lane] = bf16_lo(w[e]);
-        wsm[(8 * g + 2 * e + 1) * 33 + lane] = bf16_hi(w[e]);
+        col[(2 * e) * 33 + 8 * g] = bf16_lo(w[e]);
+        col[(2 * e + 1) * 33 + 8 * g] = bf16_hi(w[e]);
       }
     }
     __syncwarp();
-    const float mk = (m < sh.M) ? p.mask[m] : 0.f;
+    const float mk = pre.mk;
     float o0[32], o1[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -311,19 +350,19 @@ struct EpiGateSplitBwd {
       o0[i] = d * s;
       o1[i] = d * v0[i] * s * (1.f - s);
     }
-    __syncwarp();
-    if (m >= sh.M) return;
-    bf16* dp = p.d_proj5 + (int64_t)m * 5 * p.C + which * 2 * p.C + c0;  // d_p block
-    bf16* dg = dp + p.C;                                                // d_g block
+    __syncwarp();  // the transposed gradient block has been consumed: its smem is reused as staging tiles
+    const int m_base = m - lane;
+    bf16* dp = p.d_proj5 + which * 2 * p.C + c0;  // d_p block of row 0
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint4 u, w;
-      u.x = pack_bf16x2(o0[8 * i + 0], o0[8 * i + 1]); u.y = pack_bf16x2(o0[8 * i + 2], o0[8 * i + 3]);
-      u.z = pack_bf16x2(o0[8 * i + 4], o0[8 * i + 5]); u.w = pack_bf16x2(o0[8 * i + 6], o0[8 * i + 7]);
-      w.x = pack_bf16x2(o1[8 * i + 0], o1[8 * i + 1]); w.y = pack_bf16x2(o1[8 * i + 2], o1[8 * i + 3]);
-      w.z = pack_bf16x2(o1[8 * i + 4], o1[8 * i + 5]); w.w = pack_bf16x2(o1[8 * i + 6], o1[8 * i + 7]);
-      reinterpret_cast<uint4*>(dp)[i] = u;
-      reinterpret_cast<uint4*>(dg)[i] = w;
+    for (int half = 0; half < 2; ++half) {         // 0: d_p, 1: d_g (C columns further)
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        pk[i] = half ? pack_bf16x2(o1[2 * i], o1[2 * i + 1]) : pack_bf16x2(o0[2 * i], o0[2 * i + 1]);
+      bf16* blk = dp + half * p.C;
+      warp_tile_store(reinterpret_cast<uint8_t*>(wsm) + 2048 * half, lane, pk, [&](int r) -> bf16* {
+        return m_base + r < sh.M ? blk + (int64_t)(m_base + r) * 5 * p.C : nullptr;
+      });
     }
   }
 };
@@ -554,25 +593,27 @@ __global__ void __launch_bounds__(1024) trimul_colsum_fold_kernel(const float* _
 struct WgradDst {
   float* dst[5];
 };
-__global__ void __launch_bounds__(1024) trimul_wgrad_fold_kernel(const float* __restrict__ part, int n_splits, int M,
-                                                                 int C, WgradDst d) {
-  // one CTA per 32 elements: warp w adds splits w, w+32, ... in ascending order, then the 32 warp
-  // sums are added in warp order (a fixed summation tree, no atomics)
-  __shared__ float red[32][32];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int i = blockIdx.x * 32 + lane;
+__global__ void __launch_bounds__(256) trimul_wgrad_fold_kernel(const float* __restrict__ part, int n_splits, int M,
+                                                                int C, WgradDst d) {
+  // one thread per output element; the split partials are added in ascending split order (a fixed
+  // summation order, no atomics).  The loads of a batch of 8 splits are independent, so they are
+  // all in flight before the first add.
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * C) return;
+  const int64_t stride = (int64_t)M * C;
+  const float* src = part + i;
   float s = 0.f;
-  if (i < M * C)
-    for (int k = warp; k < n_splits; k += 32) s = __fadd_rn(s, part[(int64_t)k * M * C + i]);
-  red[warp][lane] = s;
-  __syncthreads();
-  if (warp == 0 && i < M * C) {
-    float t = red[0][lane];
+  int k = 0;
+  for (; k + 8 <= n_splits; k += 8) {
+    float v[8];
 #pragma unroll
-    for (int w = 1; w < 32; ++w) t = __fadd_rn(t, red[w][lane]);
-    const int row = i / C, col = i % C;
-    d.dst[row / C][(row % C) * C + col] = t;
+    for (int u = 0; u < 8; ++u) v[u] = src[(int64_t)(k + u) * stride];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) s = __fadd_rn(s, v[u]);
   }
+  for (; k < n_splits; ++k) s = __fadd_rn(s, src[(int64_t)k * stride]);
+  const int row = i / C, col = i % C;
+  d.dst[row / C][(row % C) * C + col] = s;
 }
 
 // First level of the LayerNorm-gradient fold: out[s][j] = fixed-order sum of in[s*256 .. s*256+255][j].
@@ -610,7 +651,8 @@ static int pack_weights(const float* p_in, const float* g_in, const float* p_out
   pk->W5T = base + 5 * C * C;
   pk->Wz = base + 10 * C * C;
   pk->WzT = base + 11 * C * C;
-  trimul_pack_weights_kernel<<<64, 256, 0, stream>>>(p_in, g_in, p_out, g_out, pk->W5, pk->W5T, pk->Wz, pk->WzT, C);
+  trimul_pack_weights_kernel<<<(5 * C * C + 255) / 256, 256, 0, stream>>>(p_in, g_in, p_out, g_out, pk->W5, pk->W5T,
+                                                                          pk->Wz, pk->WzT, C);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }
@@ -618,7 +660,9 @@ static int pack_weights(const float* p_in, const float* g_in, const float* p_out
 template <int C, class Epi>
 static int proj_gemm(const bf16* zln, const bf16* W5, int64_t R, int n_cols, const typename Epi::Params& ep,
                      int* status, cudaStream_t stream) {
-  using Cfg = GemmCfg<128, 2 * C, 128, false, 128, false, 4>;
+  // The gated epilogues are latency-bound: at C = 128 (four 32-column chunk pairs per tile) 16
+  // epilogue warps keep one chunk pair each in flight; narrower tiles have work for 8 only.
+  using Cfg = GemmCfg<128, 2 * C, 128, false, 128, false, (C == 128 ? 3 : 4), (C == 128 ? 16 : 8)>;
   GemmShape sh{(int)R, n_cols, C, 1, 0};
   return launch_gemm<Cfg, Epi>(zln, C, 0, W5, C, 0, sh, ep, status, stream);
 }
@@ -750,7 +794,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
   {
     WgradDst d;
     for (int i = 0; i < 5; ++i) d.dst[i] = d_p_out;
-    trimul_wgrad_fold_kernel<<<(C * C + 31) / 32, 1024, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
+    trimul_wgrad_fold_kernel<<<(C * C + 255) / 256, 256, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
     TPF_LAUNCH_OK();
   }
   // 3. output norm backward -> d_x (channel-major), d_gamma_out, d_beta_out
@@ -813,7 +857,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     d.dst[2] = d_p_in + C * C;      // b_p
     d.dst[3] = d_g_in + C * C;      // b_g
     d.dst[4] = d_g_out;             // g
-    trimul_wgrad_fold_kernel<<<(5 * C * C + 31) / 32, 1024, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
+    trimul_wgrad_fold_kernel<<<(5 * C * C + 255) / 256, 256, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
     TPF_LAUNCH_OK();
   }
   // 7. input norm backward
