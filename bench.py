@@ -152,7 +152,7 @@ class Workload:
 
     def __init__(self, dev):
         from openfold3_triangle_kernel_b200 import _cabi as C
-        from oracle.inputs import attention_inputs, trimul_inputs
+        from openfold3_triangle_kernel_b200.synthetic import attention_inputs, trimul_inputs
         self.C = C
         self.dev = dev
         B, O, H, N, D = (ATT[k] for k in "BOHND")
@@ -373,7 +373,7 @@ def run_block(args, rank, world, local_rank):
     import torch.distributed as dist
     from openfold3_triangle_kernel_b200 import dap
     from openfold3_triangle_kernel_b200.pair_block import pair_stack_block
-    from oracle.pair_block_oracle import block_params
+    from openfold3_triangle_kernel_b200.synthetic import block_params
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev) if world > 1 else dist.init_process_group(

@@ -86,7 +86,7 @@ def pair_stack_block(z, mask, params, heads, group=None):
     """TriMul outgoing -> TriMul incoming -> attention starting node -> attention ending node, each
     with its residual add.  ``z`` bf16 ``[B, N, N, C]`` (or the local rows ``[B, N/P, N, C]`` with
     ``group``); ``mask`` ``[B, N, N]`` (local rows likewise).  ``params`` as produced by
-    ``oracle.pair_block_oracle.block_params`` (fp32 masters)."""
+    ``synthetic.block_params`` (fp32 masters)."""
     if group is None:
         z = z + turbo_trimul(z, "outgoing", mask, **params["tri_mul_out"])
         z = z + turbo_trimul(z, "incoming", mask, **params["tri_mul_in"])

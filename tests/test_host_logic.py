@@ -129,3 +129,20 @@ def test_module_weight_mapping():
     m.linear_g.bias = torch.nn.Parameter(torch.zeros(32))
     with pytest.raises(ValueError, match="linear_bias"):
         tm._weights_from_module(m)
+
+
+def test_synthetic_inputs_match_the_parity_generators():
+    """The package's benchmark input generators draw the same tensors as the generators the parity
+    tests feed to the oracle (same seed -> same workload on both arms of the benchmark)."""
+    import torch
+    from openfold3_triangle_kernel_b200 import synthetic
+    from oracle import inputs as oi
+    from oracle.pair_block_oracle import block_params
+
+    a, b = synthetic.attention_inputs(1, 6, 2, 40, 16, seed=2), oi.attention_inputs(1, 6, 2, 40, 16, seed=2)
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    a, b = synthetic.trimul_inputs(1, 24, 32, seed=3), oi.trimul_inputs(1, 24, 32, seed=3)
+    assert torch.equal(a["z"], b["z"]) and torch.equal(a["mask"], b["mask"])
+    assert all(torch.equal(a["weights"][k], b["weights"][k]) for k in b["weights"])
+    a, b = synthetic.block_params(32, 2, 16, 5), block_params(32, 2, 16, 5)
+    assert all(torch.equal(a[m][k], b[m][k]) for m in b for k in b[m])
