@@ -595,25 +595,37 @@ struct WgradDst {
 };
 __global__ void __launch_bounds__(256) trimul_wgrad_fold_kernel(const float* __restrict__ part, int n_splits, int M,
                                                                 int C, WgradDst d) {
-  // one thread per output element; the split partials are added in ascending split order (a fixed
-  // summation order, no atomics).  The loads of a batch of 8 splits are independent, so they are
-  // all in flight before the first add.
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= M * C) return;
+  // 32 output elements per CTA, 8 warps.  Warp g adds its contiguous range of splits in ascending
+  // order (the loads of a batch of 8 splits are independent, so all are in flight before the first
+  // add), then the 8 range sums are added in range order: a fixed summation tree, no atomics.
+  __shared__ float red[8][32];
+  const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 32 + lane;
+  const int per = (n_splits + 7) / 8;
+  const int k0 = g * per, k1 = min(n_splits, k0 + per);
   const int64_t stride = (int64_t)M * C;
-  const float* src = part + i;
   float s = 0.f;
-  int k = 0;
-  for (; k + 8 <= n_splits; k += 8) {
-    float v[8];
+  if (i < M * C) {
+    const float* src = part + i;
+    int k = k0;
+    for (; k + 8 <= k1; k += 8) {
+      float v[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = src[(int64_t)(k + u) * stride];
+      for (int u = 0; u < 8; ++u) v[u] = src[(int64_t)(k + u) * stride];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) s = __fadd_rn(s, v[u]);
+      for (int u = 0; u < 8; ++u) s = __fadd_rn(s, v[u]);
+    }
+    for (; k < k1; ++k) s = __fadd_rn(s, src[(int64_t)k * stride]);
   }
-  for (; k < n_splits; ++k) s = __fadd_rn(s, src[(int64_t)k * stride]);
-  const int row = i / C, col = i % C;
-  d.dst[row / C][(row % C) * C + col] = s;
+  red[g][lane] = s;
+  __syncthreads();
+  if (g == 0 && i < M * C) {
+    float t = red[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t = __fadd_rn(t, red[w][lane]);
+    const int row = i / C, col = i % C;
+    d.dst[row / C][(row % C) * C + col] = t;
+  }
 }
 
 // First level of the LayerNorm-gradient fold: out[s][j] = fixed-order sum of in[s*256 .. s*256+255][j].
@@ -794,7 +806,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
   {
     WgradDst d;
     for (int i = 0; i < 5; ++i) d.dst[i] = d_p_out;
-    trimul_wgrad_fold_kernel<<<(C * C + 255) / 256, 256, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
+    trimul_wgrad_fold_kernel<<<(C * C + 31) / 32, 256, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
     TPF_LAUNCH_OK();
   }
   // 3. output norm backward -> d_x (channel-major), d_gamma_out, d_beta_out
@@ -857,7 +869,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     d.dst[2] = d_p_in + C * C;      // b_p
     d.dst[3] = d_g_in + C * C;      // b_g
     d.dst[4] = d_g_out;             // g
-    trimul_wgrad_fold_kernel<<<(5 * C * C + 255) / 256, 256, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
+    trimul_wgrad_fold_kernel<<<(5 * C * C + 31) / 32, 256, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
     TPF_LAUNCH_OK();
   }
   // 7. input norm backward
