@@ -237,24 +237,49 @@ class Workload:
 
     # ---- public API, host buffers ----------------------------------------------------------
     def e2e_step(self):
+        """One step through the public operators with HOST inputs: every input tensor of the step is
+        copied from pinned host memory (on a copy stream, so the copies of the later operators run
+        under the earlier operators' kernels), and the step's loss is read back to the host."""
         import openfold3_triangle_kernel_b200 as tk
         dev = self.dev
-        h = self.host_att
-        q, k, v, b = (h[n].to(dev, non_blocking=True).requires_grad_(True) for n in ("q", "k", "v", "pair_bias"))
-        m = h["res_mask"].to(dev, non_blocking=True)
-        out = tk.turbo_attention(q, k, v, pair_bias=b, res_mask=m)
-        loss = out.float().square().mean()
-        loss.backward()
-        total = loss.detach()
+        main = torch.cuda.current_stream()
+        if not hasattr(self, "copy_stream"):
+            self.copy_stream = torch.cuda.Stream(device=dev)
+        cs = self.copy_stream
+        start = torch.cuda.Event()
+        start.record(main)
+        cs.wait_event(start)  # the destination buffers may be blocks the previous step just released
+
+        def stage(hosts):
+            devs = [torch.empty_like(h, device=dev) for h in hosts]  # allocated in main-stream order
+            with torch.cuda.stream(cs):
+                for d, h in zip(devs, hosts):
+                    d.copy_(h, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(cs)
+            return devs, ev
+
         t = self.host_tri
-        for direction in ("outgoing", "incoming"):
-            z = t["z"].to(dev, non_blocking=True).requires_grad_(True)
-            mk = t["mask"].to(dev, non_blocking=True)
-            w = {n: x.to(dev, non_blocking=True).requires_grad_(True) for n, x in t["weights"].items()}
-            o = tk.turbo_trimul(z, direction, mk, **w)
+        wnames = list(t["weights"])
+        tri = [stage([t["z"], t["mask"]] + [t["weights"][n] for n in wnames]) for _ in range(2)]
+        h = self.host_att
+        att, att_ev = stage([h[n] for n in ("q", "k", "v", "pair_bias", "res_mask")])
+
+        total = None
+        for direction, (bufs, ev) in zip(("outgoing", "incoming"), tri):
+            main.wait_event(ev)
+            z = bufs[0].requires_grad_(True)
+            w = {n: x.requires_grad_(True) for n, x in zip(wnames, bufs[2:])}
+            o = tk.turbo_trimul(z, direction, bufs[1], **w)
             l2 = o.float().square().mean()
             l2.backward()
-            total = total + l2.detach()
+            total = l2.detach() if total is None else total + l2.detach()
+        main.wait_event(att_ev)
+        q, k, v, b = (x.requires_grad_(True) for x in att[:4])
+        out = tk.turbo_attention(q, k, v, pair_bias=b, res_mask=att[4])
+        loss = out.float().square().mean()
+        loss.backward()
+        total = total + loss.detach()
         return float(total.item())  # device -> host read of the step's result
 
     def e2e_bytes(self):
