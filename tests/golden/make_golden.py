@@ -110,7 +110,9 @@ def golden_pair_block(ref, path):
 
 
 if __name__ == "__main__":
-    ref = import_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference repository>")
+    ref = import_reference(sys.argv[1])
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     golden_attention(ref, os.path.join(HERE, "attention_cpu_case.npz"))
     for d in ("outgoing", "incoming"):
