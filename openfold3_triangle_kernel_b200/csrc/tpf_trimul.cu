@@ -434,9 +434,12 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
       xh[c][j + 1] = ok ? (bf16_hi(w[e]) - s_mu[j + 1]) * s_rs[j + 1] : 0.f;
     }
   }
-  // d_xln (row-major): 8 consecutive channels of one row per 16-byte load
+  // d_xln (row-major): 8 consecutive channels of one row per 16-byte load.  A warp takes 8 rows x 4
+  // channel groups, which makes the transposed stores below bank-conflict free (bank = 8*(lane&3) +
+  // (lane>>2) + const with the 33-word pitch).
   for (int idx = threadIdx.x; idx < TR * (C / 8); idx += 256) {
-    const int j = idx / (C / 8), c8 = idx % (C / 8);
+    const int ln = idx & 31, grp = idx >> 5;
+    const int c8 = (ln & 3) + 4 * (grp % (C / 32)), j = (ln >> 2) + 8 * (grp / (C / 32));
     uint4 u = make_uint4(0u, 0u, 0u, 0u);
     if (r0 + j < NN) u = *reinterpret_cast<const uint4*>(d_xln + ((int64_t)bb * NN + r0 + j) * C + 8 * c8);
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -467,30 +470,52 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
-    const int c = idx / (TR / 8), j8 = idx % (TR / 8);
-    if (r0 + 8 * j8 >= NN) continue;
-    const float gc = gamma[c];
-    float v[8];
+  // Four adjacent lanes share a channel (8 rows each).  The same pass forms d_x and the block's
+  // d_gamma / d_beta partials: 8-row sums in ascending row order, then the four lanes' sums in lane
+  // order (fixed order, no atomics).  Every lane of a warp takes part in the shuffles.
+  {
+    const int j8 = threadIdx.x % (TR / 8);  // the same for every idx of this thread (256 % (TR/8) == 0)
+    float rs8[8], m18[8], m28[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const int j = 8 * j8 + e;
-      v[e] = s_rs[j] * (gc * dg[c][j] - s_m1[j] - xh[c][j] * s_m2[j]);
+      rs8[e] = s_rs[8 * j8 + e];
+      m18[e] = s_m1[8 * j8 + e];
+      m28[e] = s_m2[8 * j8 + e];
     }
-    uint4 o;
-    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-    o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-    *reinterpret_cast<uint4*>(dx_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8) = o;
-  }
-  if (threadIdx.x < C) {
-    const int c = threadIdx.x;
-    float sg = 0.f, sb = 0.f;
-    for (int j = 0; j < TR; ++j) {
-      sg += dg[c][j] * xh[c][j];
-      sb += dg[c][j];
+    const bool rows_ok = r0 + 8 * j8 < NN;
+    for (int base = 0; base < C * (TR / 8); base += 256) {
+      const int idx = base + threadIdx.x;
+      const bool live = idx < C * (TR / 8);  // uniform per warp (C * TR / 8 is a multiple of 32)
+      const int c = live ? idx / (TR / 8) : 0;
+      const float gc = gamma[c];
+      float v[8], sg = 0.f, sb = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int j = 8 * j8 + e;
+        const float d = dg[c][j], x = xh[c][j];
+        v[e] = rs8[e] * (gc * d - m18[e] - x * m28[e]);
+        sg += d * x;
+        sb += d;
+      }
+      if (!live) continue;
+      if (rows_ok) {
+        uint4 o;
+        o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+        o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(dx_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8) = o;
+      }
+      const int l0 = (threadIdx.x & 31) & ~3;
+      float tg = __shfl_sync(0xffffffffu, sg, l0), tb = __shfl_sync(0xffffffffu, sb, l0);
+#pragma unroll
+      for (int k = 1; k < 4; ++k) {
+        tg += __shfl_sync(0xffffffffu, sg, l0 + k);
+        tb += __shfl_sync(0xffffffffu, sb, l0 + k);
+      }
+      if (j8 == 0) {
+        partials[(int64_t)blockIdx.x * 2 * C + c] = tg;
+        partials[(int64_t)blockIdx.x * 2 * C + C + c] = tb;
+      }
     }
-    partials[(int64_t)blockIdx.x * 2 * C + c] = sg;
-    partials[(int64_t)blockIdx.x * 2 * C + C + c] = sb;
   }
 }
 
