@@ -59,18 +59,19 @@ def trimul_forward(z, direction, mask, weights, dtype=torch.float64, eps=1e-5):
     zd = z.to(dtype)
     m = torch.ones(z.shape[:-1], dtype=dtype) if mask is None else mask.to(dtype)
     m = m.unsqueeze(-1)
+    hid = w["p_in_weight"].shape[0] // 2  # hidden width (== c in the operator contract; the stock module allows any)
     zn = F.layer_norm(zd, (c,), w["norm_in_weight"], w["norm_in_bias"], eps)
     p = F.linear(zn, w["p_in_weight"])
     g = torch.sigmoid(F.linear(zn, w["g_in_weight"]))
-    a = m * g[..., :c] * p[..., :c]
-    b = m * g[..., c:] * p[..., c:]
+    a = m * g[..., :hid] * p[..., :hid]
+    b = m * g[..., hid:] * p[..., hid:]
     if direction == "outgoing":
         x = torch.einsum("...ikc,...jkc->...ijc", a, b)
     elif direction == "incoming":
         x = torch.einsum("...kic,...kjc->...ijc", a, b)
     else:
         raise ValueError(direction)
-    xn = F.layer_norm(x, (c,), w["norm_out_weight"], w["norm_out_bias"], eps)
+    xn = F.layer_norm(x, (hid,), w["norm_out_weight"], w["norm_out_bias"], eps)
     out = F.linear(xn, w["p_out_weight"]) * torch.sigmoid(F.linear(zn, w["g_out_weight"]))
     return out
 

@@ -109,6 +109,74 @@ def golden_pair_block(ref, path):
     np.savez_compressed(path, z=z.numpy(), mask=mask.numpy(), out=x.numpy())
 
 
+def _reference_test_rng():
+    """The RNG isolation + seeding of the reference's ``seeded_rng`` fixture
+    (openfold3/tests/conftest.py:299-314)."""
+    import contextlib
+    import random
+
+    @contextlib.contextmanager
+    def ctx():
+        py_state, np_state = random.getstate(), np.random.get_state()
+        with torch.random.fork_rng():
+            torch.manual_seed(123)
+            random.seed(123)
+            np.random.seed(123)
+            yield
+        random.setstate(py_state)
+        np.random.set_state(np_state)
+
+    return ctx()
+
+
+def golden_reference_snapshots(ref, ref_root, folder):
+    """Pin against the golden vectors the reference's OWN tests hold for the two stock modules:
+    the ``ndarrays_regression`` snapshots of openfold3/tests/test_triangular_attention.py:27-72 and
+    openfold3/tests/test_triangular_multiplicative_update.py:45-86 (c_z 128, hidden 12 / 11, 4 heads,
+    batch 2, 22 residues, seed 123).  The tests' module construction and input draws are replayed
+    here, the stock module's output is checked against the committed snapshot (the reference's
+    tolerance: atol = rtol = 1e-4), and parameters + input + SNAPSHOT output of batch entry 0 are
+    stored so that the oracle can be checked against the snapshot without the reference tree."""
+    snap = os.path.join(ref_root, "openfold3", "tests", "test_data", "snapshots")
+    c_z, heads, n, batch = 128, 4, 22, 2
+    for starting in (True, False):
+        with _reference_test_rng():
+            tan = ref["TriangleAttention"](c_z, 12, heads, starting=starting)
+            for prm in tan.parameters():
+                torch.nn.init.normal_(prm, std=0.01)
+            tan.eval()
+            x = torch.rand((batch, n, n, c_z))
+            with torch.no_grad():
+                out = tan(x, chunk_size=None)
+        gold = np.load(os.path.join(snap, "test_triangular_attention", "nvidia", f"test_shape_cpu_{starting}_.npz"))["output"]
+        assert np.allclose(out.numpy(), gold, atol=1e-4, rtol=1e-4), "stock TriangleAttention does not reproduce its snapshot"
+        sd = tan.state_dict()
+        np.savez_compressed(
+            os.path.join(folder, f"reference_snapshot_triangle_attention_{'starting' if starting else 'ending'}.npz"),
+            x=x[0].numpy(), output=gold[0], ln_w=sd["layer_norm.weight"].numpy(), ln_b=sd["layer_norm.bias"].numpy(),
+            w_z=sd["linear_z.weight"].numpy(), w_q=sd["mha.linear_q.weight"].numpy(), w_k=sd["mha.linear_k.weight"].numpy(),
+            w_v=sd["mha.linear_v.weight"].numpy(), w_g=sd["mha.linear_g.weight"].numpy(), w_o=sd["mha.linear_o.weight"].numpy())
+    with _reference_test_rng():
+        tm = ref["TriangleMultiplicationOutgoing"](c_z, 11)
+        for prm in tm.parameters():
+            torch.nn.init.normal_(prm, std=0.01)
+        tm.eval()
+        x = torch.rand((batch, n, n, c_z))
+        mask = torch.randint(0, 2, size=(batch, n, n))
+        with torch.no_grad():
+            out = tm(x, mask)
+    gold = np.load(os.path.join(snap, "test_triangular_multiplicative_update", "nvidia", "test_shape_cpu_.npz"))["output"]
+    assert np.allclose(out.numpy(), gold, atol=1e-4, rtol=1e-4), "stock TriangleMultiplicationOutgoing does not reproduce its snapshot"
+    sd = tm.state_dict()
+    np.savez_compressed(
+        os.path.join(folder, "reference_snapshot_trimul_outgoing.npz"), x=x[0].numpy(), mask=mask[0].numpy(), output=gold[0],
+        norm_in_weight=sd["layer_norm_in.weight"].numpy(), norm_in_bias=sd["layer_norm_in.bias"].numpy(),
+        norm_out_weight=sd["layer_norm_out.weight"].numpy(), norm_out_bias=sd["layer_norm_out.bias"].numpy(),
+        p_in_weight=torch.cat([sd["linear_a_p.weight"], sd["linear_b_p.weight"]]).numpy(),
+        g_in_weight=torch.cat([sd["linear_a_g.weight"], sd["linear_b_g.weight"]]).numpy(),
+        p_out_weight=sd["linear_z.weight"].numpy(), g_out_weight=sd["linear_g.weight"].numpy())
+
+
 if __name__ == "__main__":
     if len(sys.argv) != 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference repository>")
@@ -118,4 +186,5 @@ if __name__ == "__main__":
     for d in ("outgoing", "incoming"):
         golden_trimul(ref, os.path.join(HERE, f"trimul_{d}_cpu_case.npz"), d)
     golden_pair_block(ref, os.path.join(HERE, "pair_block_small.npz"))
+    golden_reference_snapshots(ref, sys.argv[1], HERE)
     print("golden fixtures written to", HERE)
