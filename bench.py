@@ -80,20 +80,32 @@ def cpu_sample_seconds(att_rows=24, threads=None):
     return t_att + t_tri, threads, desc
 
 
+REFERENCE_ARM_BUDGET_S = 180.0  # wall-clock bound of the whole CPU arm, whatever --steps / --warmup ask for
+
+
 def run_reference(args, rank):
+    """CPU arm: every step is the bounded sample of cpu_sample_seconds().  One sample takes several
+    seconds, so the number of warm-up and timed samples is capped by a wall-clock budget (at least
+    one timed sample); the line states how many were timed."""
     if rank != 0:
         return
+    t_start = time.perf_counter()
     times = []
     cores, desc = None, None
-    for i in range(args.warmup + args.steps):
+    for _ in range(min(args.warmup, 1)):
+        _, cores, desc = cpu_sample_seconds()
+    per_sample = time.perf_counter() - t_start
+    while len(times) < max(1, args.steps):
+        if times and time.perf_counter() - t_start + max(per_sample, times[-1]) > REFERENCE_ARM_BUDGET_S:
+            break
         sec, cores, desc = cpu_sample_seconds()
-        if i >= args.warmup:
-            times.append(sec)
+        times.append(sec)
     sec = statistics.mean(times)
     val = STEP_FLOPS / sec / 1e12
+    desc = f"{desc}; {len(times)} timed sample(s) within a {REFERENCE_ARM_BUDGET_S:.0f} s budget"
     line = dict(impl="reference", metric=METRIC, value=val, unit="TFLOP/s", n_gpus=args.gpus, steps=args.steps,
                 warmup=args.warmup, ms_per_step=sec * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None,
-                dtype="f32", data="synthetic", config=dict(workload=WORKLOAD),
+                dtype="f32", data="synthetic", config=dict(workload=WORKLOAD), steps_timed=len(times),
                 cpu_baseline=dict(value=val, unit="TFLOP/s", cores=cores, kind="port", sample=desc),
                 e2e=dict(value=val, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
