@@ -376,7 +376,8 @@ def run_gpu(args, rank, world, local_rank):
         dom_us = stage["attn_bwd_dqkv"]
         dom_flops = 2.5 * ATT_FLOPS_FWD
         achieved = dom_flops / (dom_us * 1e-6) / 1e12
-        cpu_sec, cores, desc = cpu_sample_seconds()
+        # the CPU baseline is timed at N = 1 only (the other ranks of a multi-GPU run would sit in a barrier)
+        cpu_sec, cores, desc = cpu_sample_seconds() if world == 1 else (None, None, None)
         h2d, d2h = wl.e2e_bytes()
         line = dict(
             metric=METRIC, value=world * STEP_FLOPS / step_sec / 1e12, unit="TFLOP/s", n_gpus=world,
@@ -394,7 +395,8 @@ def run_gpu(args, rank, world, local_rank):
                           peak=peaks["bf16_tflops"], unit="TFLOP/s", frac=achieved / peaks["bf16_tflops"],
                           peak_source=peaks["source"] + " cuBLAS bf16 burst", traffic=DOMINANT_KERNEL_DRAM_BYTES,
                           algorithmic_flops_per_launch=dom_flops, launch_us=dom_us),
-            cpu_baseline=dict(value=STEP_FLOPS / cpu_sec / 1e12, unit="TFLOP/s", cores=cores, kind="port", sample=desc),
+            cpu_baseline=(dict(value=STEP_FLOPS / cpu_sec / 1e12, unit="TFLOP/s", cores=cores, kind="port", sample=desc)
+                          if cpu_sec else None),
             e2e=dict(value=world * STEP_FLOPS / e2e_sec / 1e12, unit="TFLOP/s", h2d_bytes_per_step=h2d,
                      d2h_bytes_per_step=d2h, ms_per_step=e2e_sec * 1e3),
             gpu_launches=int(launches), device_status=status, clocks=clocks)
