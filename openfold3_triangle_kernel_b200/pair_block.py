@@ -59,8 +59,10 @@ def _sharded_transpose(t, group):
     return recv.permute(1, 2, 0, 3, 4).reshape(B, N // P, N, Cc).contiguous()
 
 
-def triangle_attention_update(z, mask, p, heads, transpose_bias=False, inf=1e9, group=None):
-    """z ``[B, I(local), J, C]`` bf16, mask ``[B, I(local), J]``.  Returns the update, same shape as z."""
+def triangle_attention_update(z, mask, p, heads, transpose_bias=False, inf=1e9, group=None, attention_fn=None):
+    """z ``[B, I(local), J, C]`` bf16, mask ``[B, I(local), J]``.  Returns the update, same shape as z.
+    ``attention_fn`` replaces :func:`turbo_attention` (same signature; used to test the sharding
+    plumbing without a GPU)."""
     c = z.shape[-1]
     x = F.layer_norm(z.float(), (c,), p["ln_w"].float(), p["ln_b"].float(), 1e-5).to(z.dtype)
     mask_bias = (inf * (mask.float() - 1))[..., :, None, None, :]
@@ -75,18 +77,20 @@ def triangle_attention_update(z, mask, p, heads, transpose_bias=False, inf=1e9, 
 
     q, k, v = (heads_view(F.linear(x, p[n].to(z.dtype))) for n in ("w_q", "w_k", "w_v"))
     if group is None:
-        o = turbo_attention(q, k, v, pair_bias=bias, res_mask=mask_bias)
+        o = (attention_fn or turbo_attention)(q, k, v, pair_bias=bias, res_mask=mask_bias)
     else:
-        o = dap.axial_attention(q, k, v, bias, mask_bias, group=group)
+        o = dap.axial_attention(q, k, v, bias, mask_bias, group=group, attention_fn=attention_fn)
     gate = torch.sigmoid(F.linear(x, p["w_g"].to(z.dtype))).reshape(o.shape)
     return F.linear((o * gate).reshape(o.shape[:-2] + (heads * d,)), p["w_o"].to(z.dtype))
 
 
-def pair_stack_block(z, mask, params, heads, group=None):
+def pair_stack_block(z, mask, params, heads, group=None, trimul_backend=None, attention_fn=None):
     """TriMul outgoing -> TriMul incoming -> attention starting node -> attention ending node, each
     with its residual add.  ``z`` bf16 ``[B, N, N, C]`` (or the local rows ``[B, N/P, N, C]`` with
     ``group``); ``mask`` ``[B, N, N]`` (local rows likewise).  ``params`` as produced by
-    ``synthetic.block_params`` (fp32 masters)."""
+    ``synthetic.block_params`` (fp32 masters).  ``trimul_backend`` / ``attention_fn`` replace the
+    CUDA stage back end of :func:`dap.axial_trimul` and :func:`turbo_attention` in the sharded
+    path (used to test the collectives on CPU ranks); the defaults are the B200 operators."""
     if group is None:
         z = z + turbo_trimul(z, "outgoing", mask, **params["tri_mul_out"])
         z = z + turbo_trimul(z, "incoming", mask, **params["tri_mul_in"])
@@ -95,10 +99,11 @@ def pair_stack_block(z, mask, params, heads, group=None):
         zt = zt + triangle_attention_update(zt, mask.transpose(-1, -2), params["tri_att_end"], heads,
                                             transpose_bias=True)
         return zt.transpose(-2, -3)
-    z = z + dap.axial_trimul(z, "outgoing", mask, group=group, **params["tri_mul_out"])
-    z = z + dap.axial_trimul(z, "incoming", mask, group=group, **params["tri_mul_in"])
-    z = z + triangle_attention_update(z, mask, params["tri_att_start"], heads, group=group)
+    z = z + dap.axial_trimul(z, "outgoing", mask, group=group, backend=trimul_backend, **params["tri_mul_out"])
+    z = z + dap.axial_trimul(z, "incoming", mask, group=group, backend=trimul_backend, **params["tri_mul_in"])
+    z = z + triangle_attention_update(z, mask, params["tri_att_start"], heads, group=group, attention_fn=attention_fn)
     zt = _ShardedTranspose.apply(z, group)
     mt = _sharded_transpose(mask.unsqueeze(-1).float().contiguous(), group).squeeze(-1)
-    zt = zt + triangle_attention_update(zt, mt, params["tri_att_end"], heads, transpose_bias=True, group=group)
+    zt = zt + triangle_attention_update(zt, mt, params["tri_att_end"], heads, transpose_bias=True, group=group,
+                                        attention_fn=attention_fn)
     return _ShardedTranspose.apply(zt.contiguous(), group)

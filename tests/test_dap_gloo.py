@@ -130,6 +130,59 @@ def _worker(rank, init_file, results):
         dist.destroy_process_group()
 
 
+def _block_worker(rank, init_file, results):
+    """The whole sharded pair-stack block on two CPU ranks (fp64 stage back ends) against the
+    unsharded oracle: all-gathered bias projection, all-to-all transposes for the ending node,
+    TriMul all-to-alls, gradient of the local rows."""
+    dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=WORLD)
+    try:
+        from openfold3_triangle_kernel_b200.pair_block import _sharded_transpose, pair_stack_block
+        from oracle.pair_block_oracle import block_params, pair_block_forward
+
+        n, c, heads, d = 8, 8, 2, 4
+        g = torch.Generator().manual_seed(5)
+        z = torch.randn(1, n, n, c, generator=g, dtype=torch.float64)
+        mask = torch.ones(1, n, n, dtype=torch.float64)
+        mask[:, 6:, :] = 0
+        mask[:, :, 6:] = 0
+        dy = torch.randn(1, n, n, c, generator=g, dtype=torch.float64)
+        params = block_params(c, heads, d, 9, dtype=torch.float64)
+
+        # the sharded transpose is a global transpose of the two pair axes
+        zt = _sharded_transpose(dap.shard_rows(z, 1).contiguous(), dist.group.WORLD)
+        assert torch.equal(dap.gather_rows(zt, 1), z.transpose(1, 2))
+
+        zl = dap.shard_rows(z, 1).clone().requires_grad_(True)
+        out = pair_stack_block(zl, dap.shard_rows(mask, 1), params, heads, group=dist.group.WORLD,
+                               trimul_backend=TorchStages(), attention_fn=_attention_fn)
+        out.backward(dap.shard_rows(dy, 1))
+
+        zr = z.clone().requires_grad_(True)
+        ref = pair_block_forward(zr, mask, params, heads)
+        ref.backward(dy)
+        valid = (mask > 0)[..., None]
+        # LayerNorm of the attention wrapper runs in fp32 in the product path: fp32-level agreement
+        assert torch.allclose((dap.gather_rows(out.detach(), 1) * valid), ref.detach() * valid, atol=2e-5, rtol=2e-5)
+        assert torch.allclose(dap.gather_rows(zl.grad, 1) * valid, zr.grad * valid, atol=2e-4, rtol=2e-4)
+        results[rank] = "ok"
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        results[rank] = "".join(traceback.format_exception(e))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_pair_block_world_size_2_gloo():
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    with tempfile.TemporaryDirectory() as d:
+        init_file = os.path.join(d, "rendezvous")
+        mgr = mp.Manager()
+        results = mgr.dict()
+        mp.spawn(_block_worker, args=(init_file, results), nprocs=WORLD, join=True)
+        for r in range(WORLD):
+            assert results.get(r) == "ok", results.get(r)
+
+
 def test_axial_sharding_world_size_2_gloo():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     with tempfile.TemporaryDirectory() as d:
