@@ -146,3 +146,28 @@ def test_synthetic_inputs_match_the_parity_generators():
     assert all(torch.equal(a["weights"][k], b["weights"][k]) for k in b["weights"])
     a, b = synthetic.block_params(32, 2, 16, 5), block_params(32, 2, 16, 5)
     assert all(torch.equal(a[m][k], b[m][k]) for m in b for k in b[m])
+
+
+def test_bench_reference_arm_line_has_the_contract_keys(monkeypatch, capsys):
+    """`bench.py --impl reference` prints one JSON line with the keys the benchmark contract names;
+    the CPU sample itself is stubbed here (it takes seconds of real work)."""
+    import importlib
+    import json
+    import os
+    import types
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    monkeypatch.syspath_prepend(root)
+    bench = importlib.import_module("bench")
+    monkeypatch.setattr(bench, "cpu_sample_seconds", lambda: (2.0, 4, "stub sample"))
+    bench.run_reference(types.SimpleNamespace(gpus=1, steps=3, warmup=1), rank=0)
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better",
+                "scaling", "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
+        assert key in line, key
+    assert line["impl"] == "reference" and line["steps_timed"] == 3 and line["ms_per_step"] == 2000.0
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["cpu_baseline"]["kind"] == "port"
+    assert line["config"]["workload"] == bench.WORKLOAD
+    # ranks other than 0 print nothing
+    bench.run_reference(types.SimpleNamespace(gpus=2, steps=1, warmup=0), rank=1)
+    assert capsys.readouterr().out == ""
