@@ -8,7 +8,12 @@
  *  - All pointers are device pointers unless stated otherwise.  Nothing here
  *    allocates device memory (except where a function says so) or synchronises;
  *    work is enqueued on `stream` (a cudaStream_t passed as void*).
- *  - bf16 tensors are 16-byte aligned; extents are int64_t.
+ *  - bf16 tensors are 16-byte aligned, and so are the fp32 dbias output and every workspace
+ *    (rows are written with 16-byte vector stores); other fp32 tensors are 4-byte aligned.
+ *    A misaligned pointer is rejected with TPF_ERR_INVALID_ARGUMENT before anything is launched.
+ *    Extents are int64_t.
+ *  - Host threads may call concurrently and a process may use several GPUs: launch attributes,
+ *    symbol addresses and the SM count are cached per device.
  *  - Kernels never spin forever: a wait that exceeds its time limit records a
  *    code that tpf_device_status() returns after the stream has been synchronised.
  *
@@ -45,6 +50,16 @@ int tpf_device_status(int* status);
 
 /* Kernel launches issued through this library by the calling process so far (host counter). */
 int64_t tpf_launch_count(void);
+
+/* Self-test of the bounded wait every kernel uses: launches one 32-thread CTA that waits, with a
+ * limit of about one millisecond, on a barrier nothing arrives on.  The wait gives up, the kernel
+ * ends normally, and the next tpf_device_status() (after the stream is synchronised) reports 1
+ * (wait timeout) and clears it.  `report` (device, 3 x uint32, may be NULL) receives the SM cycles
+ * the first wait took, the cycles of a second wait in the same CTA (which must return at once) and
+ * 1 once the kernel reached its end.  The reference has no bounded waits, hence no counterpart;
+ * its kernels rely on cudaGetLastError alone
+ * (openfold3/core/kernels/turbopairformer/turbopairformer_triangle_forward.cu:1957). */
+int tpf_selftest_bounded_wait(unsigned int* report, void* stream);
 
 /* Batched bf16 GEMM  D[b][m][n] = sum_k A[b][m][k] * B[b][n][k], fp32 accumulate.
  * a_mn / b_mn = 0: operand stored [batch][mn][k] (k contiguous);

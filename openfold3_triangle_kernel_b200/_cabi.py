@@ -27,6 +27,7 @@ SIGNATURES = {
     "tpf_attn_fwd": [_P, _P, _P, _PI, _PI, _PI, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _f, _P],
     "tpf_attn_bwd_workspace_bytes": [_I, _I, _I, _I, _I, _I],
     "tpf_launch_count": [],
+    "tpf_selftest_bounded_wait": [_P, _P],
     "tpf_attn_bwd_stages": [_P, _P, _P, _P, _PI, _PI, _PI, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I,
                             _I, _I, _I, _I, _I, _f, _i, _P],
     "tpf_attn_bwd_static_scratch_capacity": [],
@@ -44,7 +45,9 @@ SIGNATURES = {
 }
 _RESTYPES = {"tpf_trimul_fwd_workspace_bytes": ctypes.c_int64, "tpf_trimul_bwd_workspace_bytes": ctypes.c_int64,
              "tpf_trimul_bwd_stages_workspace_bytes": ctypes.c_int64,
-             "tpf_attn_bwd_workspace_bytes": ctypes.c_int64, "tpf_version": ctypes.c_char_p, "tpf_last_error_string": ctypes.c_char_p}
+             "tpf_attn_bwd_workspace_bytes": ctypes.c_int64,
+             "tpf_attn_bwd_static_scratch_capacity": ctypes.c_int64, "tpf_launch_count": ctypes.c_int64,
+             "tpf_version": ctypes.c_char_p, "tpf_last_error_string": ctypes.c_char_p}
 
 ERROR_NAMES = {1: "invalid argument", 2: "unsupported", 3: "CUDA error", 4: "workspace", 5: "device status"}
 

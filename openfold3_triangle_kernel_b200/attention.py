@@ -173,6 +173,8 @@ def _attn_setup_context(ctx, inputs, output):
     out, lse = output
     ctx.save_for_backward(q, k, v, mask, bias, out, lse)
     ctx.scale = scale
+    # the log-sum-exp is a by-product for callers that ask for it, not a differentiable output
+    ctx.mark_non_differentiable(lse)
 
 
 def _attn_backward(ctx, d_out, d_lse):
@@ -200,11 +202,14 @@ def turbo_attention(q, k, v, pair_bias=None, res_mask=None, *, return_lse=False)
         if not isinstance(q, torch.Tensor) or q.ndim < 5:
             raise ValueError("unsupported TurboPairFormer case: q must have shape [*B,O,H,N,D]")
         res_mask = q.new_zeros(q.shape[:-4] + (q.shape[-4], 1, 1, q.shape[-2]), dtype=torch.float32)
-    ok, reason = is_turbo_attention_supported(q, k, v, res_mask, pair_bias)
-    if not ok:
-        raise ValueError(f"unsupported TurboPairFormer case: {reason}")
-    C.load()  # fail loudly when the native library is missing
-    _INVOCATIONS += 1
+    # Under torch.compile / torch.export the function is traced once on fake tensors: the metadata
+    # contract is checked when it runs eagerly, and by the fake kernel and the C ABI in either case.
+    if not torch.compiler.is_compiling():
+        ok, reason = is_turbo_attention_supported(q, k, v, res_mask, pair_bias)
+        if not ok:
+            raise ValueError(f"unsupported TurboPairFormer case: {reason}")
+        C.load()  # fail loudly when the native library is missing
+        _INVOCATIONS += 1
 
     prefix = tuple(q.shape[:-4])
     O, H, N, D = (int(x) for x in q.shape[-4:])

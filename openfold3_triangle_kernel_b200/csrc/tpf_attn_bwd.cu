@@ -37,6 +37,11 @@ int attn_bwd_status_fetch_and_clear(int* out) {
   return TPF_OK;
 }
 
+static int attn_bwd_status_address(int** out) {
+  static PerDeviceAddress cache;
+  return device_symbol_address(g_attn_bwd_status, cache, reinterpret_cast<void**>(out));
+}
+
 // =============================================================================================
 // kernel 0: delta[b,o,h,q] = sum_d dO[b,o,q,h,d] * O[b,o,q,h,d]      (HBM bound)
 // =============================================================================================
@@ -934,11 +939,8 @@ int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
                     cudaStream_t stream) {
   using Cfg = AttnBwdCfg<D>;
   auto kern = attn_bwd_kernel<Cfg>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-    attr_done = true;
-  }
+  static PerDeviceOnce once;  // per instantiation
+  if (int rc = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, once)) return rc;
   kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
@@ -971,9 +973,17 @@ int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out
   TPF_REQUIRE(mask_pitch >= N && mask_pitch % 4 == 0, TPF_ERR_INVALID_ARGUMENT,
               "attn_bwd: mask row pitch must be >= N and a multiple of 4 elements");
   TPF_REQUIRE(B * O * H < (1ll << 31) && N <= (1 << 24), TPF_ERR_INVALID_ARGUMENT, "attn_bwd: extent too large");
+  // dq / dk / dv rows and the delta pass's operands are accessed with 16-byte vectors
+  TPF_REQUIRE_ALIGNED16(dq, "attn_bwd", "dq");
+  TPF_REQUIRE_ALIGNED16(dk, "attn_bwd", "dk");
+  TPF_REQUIRE_ALIGNED16(dv, "attn_bwd", "dv");
+  TPF_REQUIRE_ALIGNED16(d_out, "attn_bwd", "d_out");
+  TPF_REQUIRE_ALIGNED16(out, "attn_bwd", "out");
   const int64_t need = attn_bwd_workspace_bytes(B, O, H, N, D);
   TPF_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), TPF_ERR_WORKSPACE,
               "attn_bwd: workspace of %lld bytes required, %lld given", (long long)need, (long long)workspace_bytes);
+  TPF_REQUIRE(need == 0 || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0, TPF_ERR_WORKSPACE,
+              "attn_bwd: workspace must be 16-byte aligned");
 
   // delta = rowsum(dO * O)
   if (stages & 1) {
@@ -1020,7 +1030,7 @@ int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out
   int grid = sm_count();
   if (grid > p.n_items) grid = p.n_items;
   int* status = nullptr;
-  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_attn_bwd_status));
+  if ((rc = attn_bwd_status_address(&status))) return rc;
   if (D == 16) return launch_attn_bwd<16>(tq, tk, tv, tdo, tb, tm, p, status, grid, stream);
   if (D == 32) return launch_attn_bwd<32>(tq, tk, tv, tdo, tb, tm, p, status, grid, stream);
   return launch_attn_bwd<64>(tq, tk, tv, tdo, tb, tm, p, status, grid, stream);
@@ -1032,14 +1042,9 @@ int launch_attn_dbias(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
                       cudaStream_t stream) {
   using Cfg = AttnDbiasCfg<D>;
   constexpr bool wide = true;  // 16 compute warps: measured 159 us vs 204 us with 8 at B=1, O=N=384, H=4, D=32
-  static bool attr_done = false;
-  if (!attr_done) {
-    TPF_CUDA_OK(cudaFuncSetAttribute(attn_dbias_kernel<Cfg, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Cfg::SMEM_BYTES));
-    TPF_CUDA_OK(cudaFuncSetAttribute(attn_dbias_kernel<Cfg, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Cfg::SMEM_BYTES));
-    attr_done = true;
-  }
+  static PerDeviceOnce once8, once16;  // per instantiation
+  if (int rc = ensure_dynamic_smem(attn_dbias_kernel<Cfg, 8>, Cfg::SMEM_BYTES, once8)) return rc;
+  if (int rc = ensure_dynamic_smem(attn_dbias_kernel<Cfg, 16>, Cfg::SMEM_BYTES, once16)) return rc;
   if (wide) attn_dbias_kernel<Cfg, 16><<<grid, 640, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
   else attn_dbias_kernel<Cfg, 8><<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
   TPF_LAUNCH_OK();
@@ -1071,6 +1076,7 @@ int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_ou
                    float* dbias, void* workspace, int64_t workspace_bytes, int64_t B, int64_t O, int64_t H, int64_t N,
                    int64_t D, float scale, cudaStream_t stream) {
   TPF_REQUIRE(dbias != nullptr, TPF_ERR_INVALID_ARGUMENT, "attn_bwd: dbias is NULL");
+  TPF_REQUIRE_ALIGNED16(dbias, "attn_bwd", "dbias");  // rows are written with float4 stores
   const int64_t G = bias_batch;
   int n_chunks, chunk_len;
   dbias_plan(B, O, H, N, G, &n_chunks, &chunk_len);
@@ -1078,6 +1084,8 @@ int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_ou
   TPF_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), TPF_ERR_WORKSPACE,
               "attn_bwd: dBias workspace of %lld bytes required, %lld given", (long long)need,
               (long long)workspace_bytes);
+  TPF_REQUIRE(need == 0 || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0, TPF_ERR_WORKSPACE,
+              "attn_bwd: dBias workspace must be 16-byte aligned");
   const int swz = 2 * (int)D;
   CUtensorMap tq, tk, tv, tdo, tb, tm;
   int rc;
@@ -1103,7 +1111,7 @@ int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_ou
   const int64_t grid = (int64_t)G * H * p.q_tiles * p.k_tiles * n_chunks;
   TPF_REQUIRE(grid < (1ll << 31), TPF_ERR_INVALID_ARGUMENT, "attn_bwd: dBias grid too large");
   int* status = nullptr;
-  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_attn_bwd_status));
+  if ((rc = attn_bwd_status_address(&status))) return rc;
   if (D == 16) rc = launch_attn_dbias<16>(tq, tk, tv, tdo, tb, tm, p, status, (int)grid, stream);
   else if (D == 32) rc = launch_attn_dbias<32>(tq, tk, tv, tdo, tb, tm, p, status, (int)grid, stream);
   else rc = launch_attn_dbias<64>(tq, tk, tv, tdo, tb, tm, p, status, (int)grid, stream);
@@ -1135,21 +1143,11 @@ int64_t attn_bwd_static_scratch_capacity() { return kStaticScratchBytes; }
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
 // address is looked up once per device (with that device current) and cached.
 static int static_scratch_address(void** out) {
-  constexpr int kMaxDevices = 64;
-  static void* addr[kMaxDevices] = {};
-  static std::atomic<bool> ready[kMaxDevices] = {};
-  int dev = 0;
-  TPF_CUDA_OK(cudaGetDevice(&dev));
-  TPF_REQUIRE(dev >= 0 && dev < kMaxDevices, TPF_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  if (!ready[dev].load(std::memory_order_acquire)) {
-    void* p = nullptr;
-    TPF_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
-    TPF_REQUIRE(p != nullptr && (reinterpret_cast<uintptr_t>(p) & 255) == 0, TPF_ERR_CUDA,
-                "static scratch address lookup returned a bad pointer");
-    addr[dev] = p;
-    ready[dev].store(true, std::memory_order_release);
-  }
-  *out = addr[dev];
+  static PerDeviceAddress cache;
+  int rc = device_symbol_address(g_static_scratch, cache, out);
+  if (rc) return rc;
+  TPF_REQUIRE((reinterpret_cast<uintptr_t>(*out) & 255) == 0, TPF_ERR_CUDA,
+              "static scratch address lookup returned a misaligned pointer");
   return TPF_OK;
 }
 

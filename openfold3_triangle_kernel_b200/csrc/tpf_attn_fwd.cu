@@ -526,11 +526,8 @@ int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
                     const CUtensorMap& tmk, const AttnFwdParams& p, int* status, cudaStream_t stream) {
   using Cfg = AttnFwdCfg<D, NKV>;
   auto kern = attn_fwd_kernel<Cfg>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-    attr_done = true;
-  }
+  static PerDeviceOnce once;  // per instantiation
+  if (int rc = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, once)) return rc;
   int grid = sm_count();
   if (grid > p.n_items) grid = p.n_items;
   kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tb, tmk, p, status);
@@ -552,7 +549,8 @@ int attn_fwd(const void* q, const void* k, const void* v, const int64_t* q_strid
   TPF_REQUIRE(mask_pitch >= N && mask_pitch % 4 == 0, TPF_ERR_INVALID_ARGUMENT,
               "attn_fwd: mask row pitch must be >= N and a multiple of 4 elements");
   TPF_REQUIRE(N <= (1 << 24) && B * O * H < (1ll << 31), TPF_ERR_INVALID_ARGUMENT, "attn_fwd: extent too large");
-  TPF_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, TPF_ERR_INVALID_ARGUMENT, "attn_fwd: out must be 16-byte aligned");
+  TPF_REQUIRE_ALIGNED16(out, "attn_fwd", "out");
+  TPF_REQUIRE((reinterpret_cast<uintptr_t>(lse) & 3) == 0, TPF_ERR_INVALID_ARGUMENT, "attn_fwd: lse must be 4-byte aligned");
   const int swz = 2 * (int)D;
   CUtensorMap tq, tk, tv, tb, tm;
   int rc;
@@ -574,7 +572,10 @@ int attn_fwd(const void* q, const void* k, const void* v, const int64_t* q_strid
   TPF_REQUIRE(items < (1ll << 31), TPF_ERR_INVALID_ARGUMENT, "attn_fwd: too many work items");
   p.n_items = (int)items;
   int* status = nullptr;
-  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_attn_fwd_status));
+  {
+    static PerDeviceAddress cache;
+    if ((rc = device_symbol_address(g_attn_fwd_status, cache, reinterpret_cast<void**>(&status)))) return rc;
+  }
   if (D == 16) return launch_attn_fwd<16, 2>(tq, tk, tv, tb, tm, p, status, stream);
   if (D == 32) return launch_attn_fwd<32, 2>(tq, tk, tv, tb, tm, p, status, stream);
   return launch_attn_fwd<64, 1>(tq, tk, tv, tb, tm, p, status, stream);

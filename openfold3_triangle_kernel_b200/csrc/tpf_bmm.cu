@@ -40,7 +40,10 @@ int bmm_bf16(const void* A, int64_t lda, int64_t bsa, int a_mn, const void* B, i
               "bmm: k_per_split must be a non-negative multiple of 64");
   GemmShape sh{(int)M, (int)N, (int)K, (int)batch, (int)k_per_split};
   int* status = nullptr;
-  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_bmm_status));
+  {
+    static PerDeviceAddress cache;
+    if (int rc = device_symbol_address(g_bmm_status, cache, reinterpret_cast<void**>(&status))) return rc;
+  }
 #define TPF_BMM_CASE(SWZ, AM, BM)                                                                              \
   if (swizzle_bytes == SWZ && (a_mn != 0) == AM && (b_mn != 0) == BM)                                          \
     return out_f32 ? bmm_dispatch<SWZ, AM, BM, float>(A, lda, bsa, B, ldb, bsb, D, ldd, bsd, sh, status, stream) \

@@ -40,6 +40,9 @@ int attn_bwd_static_scratch(const void* q, const void* k, const void* v, const v
                             const float* mask, int64_t mask_pitch, const void* bias, int64_t bias_pitch,
                             int64_t bias_batch, void* dq, void* dk, void* dv, float* dbias, float* delta, int64_t B,
                             int64_t O, int64_t H, int64_t N, int64_t D, float scale, cudaStream_t stream);
+int selftest_status_fetch_and_clear(int* out);
+int selftest_bounded_wait(unsigned int* report, cudaStream_t stream);
+
 int trimul_status_fetch_and_clear(int* out);
 int64_t trimul_fwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
 int64_t trimul_bwd_workspace_bytes(int64_t B, int64_t N, int64_t C);
@@ -79,8 +82,14 @@ int tpf_device_status(int* status) {
   total |= v;
   if ((rc = tpf::trimul_status_fetch_and_clear(&v))) return rc;
   total |= v;
+  if ((rc = tpf::selftest_status_fetch_and_clear(&v))) return rc;
+  total |= v;
   *status = total;
   return TPF_OK;
+}
+
+int tpf_selftest_bounded_wait(unsigned int* report, void* stream) {
+  return tpf::selftest_bounded_wait(report, static_cast<cudaStream_t>(stream));
 }
 
 int tpf_bmm_bf16(const void* A, int64_t lda, int64_t batch_stride_a, int a_mn, const void* B, int64_t ldb,

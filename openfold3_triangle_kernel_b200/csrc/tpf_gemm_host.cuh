@@ -35,11 +35,8 @@ int launch_gemm(const void* A, int64_t lda, int64_t bsa, const void* B, int64_t 
   auto kern = gemm_umma_kernel<Cfg, Epi>;
   constexpr int smem_bytes = Cfg::SMEM_BYTES + Cfg::EPI_WARPS * Epi::kSmemPerWarp;
   static_assert(smem_bytes <= 232448, "shared memory budget");
-  static bool attr_done = false;  // per instantiation
-  if (!attr_done) {
-    TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    attr_done = true;
-  }
+  static PerDeviceOnce once;  // per instantiation
+  if ((rc = ensure_dynamic_smem(kern, smem_bytes, once))) return rc;
   const int mt = (sh.M + Cfg::BM - 1) / Cfg::BM, nt = (sh.N + Cfg::BN - 1) / Cfg::BN;
   const int tiles = sh.batch * mt * nt;
   int grid = sm_count();

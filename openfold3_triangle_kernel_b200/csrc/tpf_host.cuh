@@ -112,13 +112,67 @@ inline int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uin
   return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes, box, 0);
 }
 
-inline int sm_count() {
-  static int n = 0;
-  if (n) return n;
+// ---- per-device host state --------------------------------------------------------------
+// Function attributes, symbol addresses and the SM count belong to a device, not to the process;
+// a process may drive several GPUs from several host threads.  Each cache below is a small table
+// indexed by device ordinal whose entries are published with release / acquire ordering (two
+// threads that race on the first use both do the idempotent set-up, then one flag store wins).
+constexpr int kMaxDevices = 64;
+
+inline int current_device(int* dev) {
+  TPF_CUDA_OK(cudaGetDevice(dev));
+  TPF_REQUIRE(*dev >= 0 && *dev < kMaxDevices, TPF_ERR_UNSUPPORTED, "device ordinal %d out of range", *dev);
+  return TPF_OK;
+}
+
+struct PerDeviceOnce {
+  std::atomic<bool> done[kMaxDevices];
+};
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize for `kern` on the current device, once per device.
+template <class Kernel>
+inline int ensure_dynamic_smem(Kernel kern, int bytes, PerDeviceOnce& once) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  int rc = current_device(&dev);
+  if (rc) return rc;
+  if (once.done[dev].load(std::memory_order_acquire)) return TPF_OK;
+  TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  once.done[dev].store(true, std::memory_order_release);
+  return TPF_OK;
+}
+
+// Device address of a __device__ symbol on the current device, looked up once per device.
+struct PerDeviceAddress {
+  std::atomic<void*> addr[kMaxDevices];
+};
+template <class Symbol>
+inline int device_symbol_address(const Symbol& sym, PerDeviceAddress& cache, void** out) {
+  int dev = 0;
+  int rc = current_device(&dev);
+  if (rc) return rc;
+  void* p = cache.addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    TPF_CUDA_OK(cudaGetSymbolAddress(&p, sym));
+    TPF_REQUIRE(p != nullptr, TPF_ERR_CUDA, "symbol address lookup returned NULL");
+    cache.addr[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return TPF_OK;
+}
+
+inline int sm_count() {
+  static std::atomic<int> table[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = table[dev].load(std::memory_order_acquire);
+  if (n > 0) return n;
   if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  table[dev].store(n, std::memory_order_release);
   return n;
 }
+
+#define TPF_REQUIRE_ALIGNED16(ptr, who, name)                                                       \
+  TPF_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, TPF_ERR_INVALID_ARGUMENT,               \
+              "%s: %s must be 16-byte aligned", who, name)
 
 }  // namespace tpf

@@ -839,11 +839,8 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     const int tiles = (int)((NN + 31) / 32);
     auto kern = trimul_xnorm_bwd_kernel<C>;
     const int smem = 2 * C * 33 * 4;
-    static bool attr_done = false;
-    if (!attr_done) {
-      TPF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      attr_done = true;
-    }
+    static PerDeviceOnce once;  // per instantiation
+    if ((rc = ensure_dynamic_smem(kern, smem, once))) return rc;
     kern<<<(unsigned)(B * tiles), 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out,
                                                        NN, tiles);
     TPF_LAUNCH_OK();
@@ -957,7 +954,10 @@ int trimul_fwd(const void* z, const float* mask, const float* p_in, const float*
   TPF_REQUIRE(workspace && workspace_bytes >= trimul_fwd_workspace_bytes(B, N, C), TPF_ERR_WORKSPACE,
               "trimul_fwd: workspace of %lld bytes required", (long long)trimul_fwd_workspace_bytes(B, N, C));
   int* status = nullptr;
-  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_trimul_status));
+  {
+    static PerDeviceAddress cache;
+    if ((rc = device_symbol_address(g_trimul_status, cache, reinterpret_cast<void**>(&status)))) return rc;
+  }
   TrimulPacked pk;
   if ((rc = pack_weights(p_in, g_in, p_out, g_out, workspace, (int)C, &pk, stream))) return rc;
 #define TPF_TRIMUL_FWD(CC)                                                                                         \
@@ -994,7 +994,10 @@ int trimul_bwd(const void* d_out, const void* z, const float* mask, const float*
               TPF_ERR_WORKSPACE, "trimul_bwd: 256-byte aligned workspace of %lld bytes required",
               (long long)trimul_bwd_workspace_bytes(B, NN, C));
   int* status = nullptr;
-  TPF_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_trimul_status));
+  {
+    static PerDeviceAddress cache;
+    if ((rc = device_symbol_address(g_trimul_status, cache, reinterpret_cast<void**>(&status)))) return rc;
+  }
 #define TPF_TRIMUL_BWD(CC)                                                                                            \
   if (C == CC)                                                                                                        \
     return trimul_bwd_t<CC>((const bf16*)d_out, (const bf16*)z, mask, p_in, g_in, p_out, g_out, gin, gout, incoming,  \

@@ -49,29 +49,47 @@ def gather_rows(t, dim, group=None):
     return torch.cat(parts, dim=dim)
 
 
-def rows_to_channels(t, group=None):
-    """``[B, C, N_local, N]`` (rows of this rank, all channels) -> ``[B, C/P, N, N]``
-    (all rows, channels of this rank).  One all-to-all."""
+def rows_to_channels_many(ts, group=None):
+    """Each ``t`` of ``ts``: ``[B, C, N_local, N]`` (rows of this rank, all channels) ->
+    ``[B, C/P, N, N]`` (all rows, channels of this rank).  ONE all-to-all moves all of them: the
+    tensors travel stacked in one send buffer, so a / b (and d_a / d_b on the way back) cost one
+    collective launch instead of one each."""
     P, _ = _world(group)
-    B, Cc, Nl, N = t.shape
+    B, Cc, Nl, N = ts[0].shape
     if Cc % P:
         raise ValueError(f"C={Cc} is not divisible by the group size {P}")
-    send = t.reshape(B, P, Cc // P, Nl, N).permute(1, 0, 2, 3, 4).contiguous()
+    K = len(ts)
+    send = ts[0].new_empty((P, K, B, Cc // P, Nl, N))
+    for i, t in enumerate(ts):
+        send[:, i].copy_(t.reshape(B, P, Cc // P, Nl, N).permute(1, 0, 2, 3, 4))
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
-    return recv.permute(1, 2, 0, 3, 4).reshape(B, Cc // P, P * Nl, N).contiguous()
+    return [recv[:, i].permute(1, 2, 0, 3, 4).reshape(B, Cc // P, P * Nl, N) for i in range(K)]
+
+
+def channels_to_rows_many(ts, group=None):
+    """Inverse of :func:`rows_to_channels_many`: each ``[B, C/P, N, N]`` -> ``[B, C, N_local, N]``."""
+    P, _ = _world(group)
+    B, Cl, Nf, N = ts[0].shape
+    if Nf % P:
+        raise ValueError(f"N={Nf} is not divisible by the group size {P}")
+    K = len(ts)
+    send = ts[0].new_empty((P, K, B, Cl, Nf // P, N))
+    for i, t in enumerate(ts):
+        send[:, i].copy_(t.reshape(B, Cl, P, Nf // P, N).permute(2, 0, 1, 3, 4))
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return [recv[:, i].permute(1, 0, 2, 3, 4).reshape(B, P * Cl, Nf // P, N) for i in range(K)]
+
+
+def rows_to_channels(t, group=None):
+    """``[B, C, N_local, N]`` -> ``[B, C/P, N, N]``.  One all-to-all."""
+    return rows_to_channels_many([t], group)[0]
 
 
 def channels_to_rows(t, group=None):
     """Inverse of :func:`rows_to_channels`: ``[B, C/P, N, N]`` -> ``[B, C, N_local, N]``."""
-    P, _ = _world(group)
-    B, Cl, Nf, N = t.shape
-    if Nf % P:
-        raise ValueError(f"N={Nf} is not divisible by the group size {P}")
-    send = t.reshape(B, Cl, P, Nf // P, N).permute(2, 0, 1, 3, 4).contiguous()
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)
-    return recv.permute(1, 0, 2, 3, 4).reshape(B, P * Cl, Nf // P, N).contiguous()
+    return channels_to_rows_many([t], group)[0]
 
 
 class _SumGradOverRanks(torch.autograd.Function):
@@ -115,19 +133,33 @@ class CudaTrimulStages:
     """Stage functions of the sharded TriMul on ``libtpf_b200.so``.  All tensors are bf16 / fp32 on
     one CUDA device; ``rows`` = ``N_local * N`` must be a multiple of 64."""
 
+    def __init__(self, reuse_buffers=False):
+        # reuse_buffers: keep one set of stage buffers per (shape, direction) and hand it out again on
+        # the next forward.  Only for callers that finish the backward of a shape/direction before
+        # they start its next forward (a benchmark loop); autograd users keep the default.
+        self._reuse = bool(reuse_buffers)
+        self._cache = {}
+
     def proj_fwd(self, z, mask, w, incoming):
         B, Nl, N, Cc = z.shape
         dev = z.device
         R = B * Nl * N
-        bf = lambda *s: torch.empty(s, device=dev, dtype=torch.bfloat16)  # noqa: E731
-        f32 = lambda *s: torch.empty(s, device=dev, dtype=torch.float32)  # noqa: E731
-        st = dict(z=z.contiguous(), mask=mask.to(torch.float32).contiguous(),
-                  w={k: w[k].detach().float().contiguous() for k in _W_FWD}, incoming=bool(incoming),
-                  zln=bf(R, Cc), gate=bf(R, Cc), mean_in=f32(R), rstd_in=f32(R),
-                  a_cm=bf(B, Cc, Nl, N), b_cm=bf(B, Cc, Nl, N),
-                  x_cm=None, xln=bf(R, Cc), mean_out=f32(R), rstd_out=f32(R), out=bf(B, Nl, N, Cc))
-        nbytes = max(C.load().tpf_trimul_fwd_workspace_bytes(B, N, Cc), 256)
-        st["ws_f"] = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+        key = (B, Nl, N, Cc, bool(incoming), dev)
+        st = self._cache.get(key) if self._reuse else None
+        if st is None:
+            bf = lambda *s: torch.empty(s, device=dev, dtype=torch.bfloat16)  # noqa: E731
+            f32 = lambda *s: torch.empty(s, device=dev, dtype=torch.float32)  # noqa: E731
+            st = dict(incoming=bool(incoming), zln=bf(R, Cc), gate=bf(R, Cc), mean_in=f32(R), rstd_in=f32(R),
+                      a_cm=bf(B, Cc, Nl, N), b_cm=bf(B, Cc, Nl, N),
+                      x_cm=None, xln=bf(R, Cc), mean_out=f32(R), rstd_out=f32(R), out=bf(B, Nl, N, Cc))
+            nbytes = max(C.load().tpf_trimul_fwd_workspace_bytes(B, N, Cc), 256)
+            st["ws_f"] = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+            if self._reuse:
+                self._cache[key] = st
+        st["x_cm"] = None
+        st["z"] = z.contiguous()
+        st["mask"] = mask.to(torch.float32).contiguous()
+        st["w"] = {k: w[k].detach().float().contiguous() for k in _W_FWD}
         self._fwd(st, 1)
         return st
 
@@ -197,7 +229,8 @@ class CudaTrimulStages:
 
     def out_bwd(self, st, d_out):
         B, Nl, N, Cc = st["z"].shape
-        st["dx"] = torch.empty(B, Cc, Nl, N, device=st["z"].device, dtype=torch.bfloat16)
+        if st.get("dx") is None:
+            st["dx"] = torch.empty(B, Cc, Nl, N, device=st["z"].device, dtype=torch.bfloat16)
         st["d_out"] = d_out.to(torch.bfloat16).contiguous()
         self._bwd(st, st["d_out"], 1, st["dx"], None, None)
         return st["dx"]
@@ -214,40 +247,52 @@ _WNAMES = ("norm_in_weight", "norm_in_bias", "p_in_weight", "g_in_weight", "norm
            "p_out_weight", "g_out_weight")
 
 
+def axial_trimul_forward(z, mask, incoming, group, backend, w):
+    """Forward of the row-sharded TriMul without autograd: returns ``(out, state)``; ``state`` feeds
+    :func:`axial_trimul_backward`.  Collectives: one all-to-all for a and b together (rows ->
+    channels), one for x (channels -> rows)."""
+    st = backend.proj_fwd(z, mask, w, incoming)
+    a_c, b_c = rows_to_channels_many([st["a_cm"], st["b_cm"]], group)
+    x_c = backend.contract(a_c, b_c, incoming)
+    x_r = channels_to_rows(x_c, group)
+    out = backend.out_fwd(st, x_r)
+    return out, dict(st=st, a_c=a_c, b_c=b_c, group=group, backend=backend, incoming=incoming)
+
+
+def axial_trimul_backward(state, d_out):
+    """Backward of :func:`axial_trimul_forward`: returns ``(d_z, grads)`` with ``grads`` a dict of fp32
+    weight / LayerNorm gradients already summed over the ranks.  Collectives: one all-to-all for d_x,
+    one for d_a and d_b together, one flat all-reduce of the weight gradients."""
+    be, group = state["backend"], state["group"]
+    dx_r = be.out_bwd(state["st"], d_out)
+    dx_c = rows_to_channels(dx_r, group)
+    da_c, db_c = be.contract_bwd(dx_c, state["a_c"], state["b_c"], state["incoming"])
+    da_r, db_r = channels_to_rows_many([da_c, db_c], group)
+    d_z, grads = be.proj_bwd(state["st"], da_r, db_r)
+    # weight / LayerNorm gradients are sums over ALL pair rows: one flat all-reduce
+    flat = torch.cat([grads[n].reshape(-1).float() for n in _WNAMES])
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+    outs, off = {}, 0
+    for n in _WNAMES:
+        k = grads[n].numel()
+        outs[n] = flat[off:off + k].reshape(grads[n].shape)
+        off += k
+    return d_z, outs
+
+
 class _AxialTriMul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, z, mask, incoming, group, backend, *wlist):
-        w = dict(zip(_WNAMES, wlist))
-        st = backend.proj_fwd(z, mask, w, incoming)
-        a_c = rows_to_channels(st["a_cm"], group)
-        b_c = rows_to_channels(st["b_cm"], group)
-        x_c = backend.contract(a_c, b_c, incoming)
-        x_r = channels_to_rows(x_c, group)
-        out = backend.out_fwd(st, x_r)
-        ctx.st, ctx.a_c, ctx.b_c = st, a_c, b_c
-        ctx.group, ctx.backend, ctx.incoming = group, backend, incoming
+        out, state = axial_trimul_forward(z, mask, incoming, group, backend, dict(zip(_WNAMES, wlist)))
+        ctx.state = state
         ctx.wdtypes = [t.dtype for t in wlist]
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        be, group = ctx.backend, ctx.group
-        dx_r = be.out_bwd(ctx.st, d_out)
-        dx_c = rows_to_channels(dx_r, group)
-        da_c, db_c = be.contract_bwd(dx_c, ctx.a_c, ctx.b_c, ctx.incoming)
-        da_r = channels_to_rows(da_c, group)
-        db_r = channels_to_rows(db_c, group)
-        d_z, grads = be.proj_bwd(ctx.st, da_r, db_r)
-        # weight / LayerNorm gradients are sums over ALL pair rows: one flat all-reduce
-        flat = torch.cat([grads[n].reshape(-1).float() for n in _WNAMES])
-        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
-        outs, off = [], 0
-        for n, dt in zip(_WNAMES, ctx.wdtypes):
-            k = grads[n].numel()
-            outs.append(flat[off:off + k].reshape(grads[n].shape).to(dt))
-            off += k
-        ctx.st = ctx.a_c = ctx.b_c = None
-        return (d_z, None, None, None, None, *outs)
+        d_z, grads = axial_trimul_backward(ctx.state, d_out)
+        ctx.state = None
+        return (d_z, None, None, None, None, *[grads[n].to(dt) for n, dt in zip(_WNAMES, ctx.wdtypes)])
 
 
 def axial_trimul(z, direction="outgoing", mask=None, *, group=None, backend=None, **weights):

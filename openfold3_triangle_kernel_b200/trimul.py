@@ -249,10 +249,13 @@ def turbo_trimul(z, direction="outgoing", mask=None, *, generator=None, **weight
     unknown = set(weights) - set(_WEIGHT_NAMES)
     if unknown:
         raise TypeError(f"turbo_trimul got unexpected keyword arguments {sorted(unknown)}")
-    res = check_trimul_support(z, direction, mask, weights)
-    if not res.supported:
-        raise ValueError(f"turbo_trimul unsupported [{res.code}]: {res.reason}")
-    C.load()
+    # Under torch.compile / torch.export the function is traced once on fake tensors: the metadata
+    # contract is checked when it runs eagerly, and by the fake kernel and the C ABI in either case.
+    if not torch.compiler.is_compiling():
+        res = check_trimul_support(z, direction, mask, weights)
+        if not res.supported:
+            raise ValueError(f"turbo_trimul unsupported [{res.code}]: {res.reason}")
+        C.load()
 
     c = int(z.shape[-1])
     n = int(z.shape[-2])

@@ -173,6 +173,14 @@ def test_training_shape_full_size_properties():
     for n in ("out", "dq", "dk", "dv"):
         assert ao.rel_l2(got[n][:, sub], ref[n]) <= 6e-3, n
     assert (got["lse"][:, sub].double() - ref["lse"].double()).abs().max().item() <= LSE_TOL * 10
+    # dBias depends on ALL 384 outer rows and on the chunk plan (o-chunks + fold at this shape): compare it
+    # with the oracle's sum over every row, accumulated chunk by chunk in fp32
+    dbias_ref = torch.zeros_like(inp["pair_bias"], dtype=torch.float32)
+    for o0 in range(0, 384, 48):
+        sl = slice(o0, o0 + 48)
+        part = {k: (v[:, sl] if k != "pair_bias" else v) for k, v in inp.items()}
+        dbias_ref += _oracle(part, d_out[:, sl], dtype=torch.float32)["dbias"]
+    assert ao.rel_l2(got["dbias"], dbias_ref) <= 6e-3
     # dS rows sum to zero => dbias rows sum to zero up to rounding of the summands
     db = got["dbias"].float()
     assert db.sum(-1).abs().max().item() <= 2e-2 * db.abs().sum(-1).max().item()

@@ -47,6 +47,17 @@ def test_argument_validation_needs_no_device():
         C.call("tpf_attn_fwd", one, one, one, st, st, st, one, 8, one, 8, 1, one, one, 1, 1, 1, 8, 24, 1.0, null)
     with pytest.raises(ValueError, match="bias row pitch"):
         C.call("tpf_attn_fwd", one, one, one, st, st, st, one, 8, one, 7, 1, one, one, 1, 1, 1, 7, 32, 1.0, null)
+    # pointers that the kernels access with 16-byte vectors must be 16-byte aligned
+    mis = ctypes.c_void_p(264)
+    with pytest.raises(ValueError, match="out must be 16-byte aligned"):
+        C.call("tpf_attn_fwd", one, one, one, st, st, st, one, 8, one, 8, 1, mis, one, 1, 1, 1, 8, 32, 1.0, null)
+    bwd = lambda dq, dbias, stages: C.call(  # noqa: E731
+        "tpf_attn_bwd_stages", one, one, one, one, st, st, st, one, one, one, 8, one, 8, 1, dq, one, one, dbias, one,
+        null, 0, 1, 1, 1, 8, 32, 1.0, stages, null)
+    with pytest.raises(ValueError, match="dq must be 16-byte aligned"):
+        bwd(mis, one, 2)
+    with pytest.raises(ValueError, match="dbias must be 16-byte aligned"):
+        bwd(one, mis, 4)
     args = [one] * 10 + [0, 1, 12, 128] + [one] * 12 + [1 << 20, null]
     with pytest.raises(ValueError, match="multiple of 8"):
         C.call("tpf_trimul_fwd", *args)

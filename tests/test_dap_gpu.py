@@ -1,5 +1,6 @@
 """Axial sharding on the CUDA back end: a one-rank group must reproduce the unsharded operators,
 and (when two GPUs are visible) a two-rank NCCL run must reproduce the CPU oracle."""
+import datetime
 import os
 import tempfile
 
@@ -29,7 +30,8 @@ def _worker(rank, world, init_file, results):
     from oracle.inputs import attention_inputs
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
     try:
         inp = _case()
         for direction in ("outgoing", "incoming"):

@@ -159,7 +159,7 @@ def test_bench_reference_arm_line_has_the_contract_keys(monkeypatch, capsys):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     monkeypatch.syspath_prepend(root)
     bench = importlib.import_module("bench")
-    monkeypatch.setattr(bench, "cpu_sample_seconds", lambda: (2.0, 4, "stub sample"))
+    monkeypatch.setattr(bench, "cpu_step_seconds", lambda: (2.0, 4, "stub sample"))
     bench.run_reference(types.SimpleNamespace(gpus=1, steps=3, warmup=1), rank=0)
     line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better",
