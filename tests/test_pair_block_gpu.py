@@ -34,8 +34,8 @@ def _oracle(cfg, z, mask, d_out, params):
     """fp64 oracle for the small case, fp32 for the large one (memory); returns plain tensors."""
     from oracle.pair_block_oracle import pair_block_forward
     dt = torch.float64 if cfg[0] <= 128 else torch.float32
-    zz = z.to(dt).requires_grad_(True)
-    pp = {k: {n: t.to(dt).requires_grad_(True) for n, t in v.items()} for k, v in params.items()}
+    zz = z.detach().clone().to(dt).requires_grad_(True)
+    pp = {k: {n: t.detach().clone().to(dt).requires_grad_(True) for n, t in v.items()} for k, v in params.items()}
     out = pair_block_forward(zz, mask, pp, cfg[2], dtype=dt)
     out.backward(d_out.to(dt))
     return dict(out=out.detach(), dz=zz.grad, grads={k: {n: t.grad for n, t in v.items()} for k, v in pp.items()})
