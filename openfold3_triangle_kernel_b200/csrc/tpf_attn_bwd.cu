@@ -97,6 +97,9 @@ struct AttnBwdCfg {
   static constexpr int KS = D <= 32 ? 3 : 1;   // key tiles whose dK/dV stay in TMEM together
   static constexpr int NKV = 2, NQ = 2;
   static constexpr int NB = D <= 32 ? 2 : 1;   // bias stages
+  static constexpr int NCW = 16;               // compute warps: four threads per query row, 32 keys each
+  static constexpr int THREADS = 32 * (NCW + 2);
+  static constexpr int WARP_TMA = NCW, WARP_MMA = NCW + 1;
   static constexpr int SWZ = 2 * D;
   static constexpr int TILE = 128 * D * 2;
   static constexpr int BIAS_STAGE = 32768, PD_BYTES = 32768;
@@ -109,7 +112,7 @@ struct AttnBwdCfg {
   static constexpr int OFF_V = OFF_K + NKV * TILE;       // [NKV]
   static constexpr int OFF_MASK = OFF_V + NKV * TILE;    // [NKV] x 512
   static constexpr int OFF_BAR = OFF_MASK + NKV * 512;
-  static constexpr int N_BAR = 2 * NB + 2 * NQ + 2 * NKV + 10;
+  static constexpr int N_BAR = 2 * NB + 2 * NQ + 2 * NKV + 6;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
   static constexpr int TM_S = 0, TM_DP = 128, TM_DQ = 256, TM_DK = 320, TM_DV = 320 + KS * D;
   static constexpr int TMEM_COLS = 512;
@@ -143,13 +146,18 @@ struct BwdWalk {
   }
 };
 
+// Sixteen compute warps: thread (row, part) owns query row `row` (= TMEM lane) and the 32 keys
+// [32 part, 32 part + 32) of a 128 x 128 tile.  It walks them 16 columns at a time straight from
+// TMEM (S and dP), forms P and dS, and keeps the bf16 results packed in 32 registers; only the
+// shared-memory stores wait for the UMMAs of the previous tile to release the P / dS tiles, so
+// the arithmetic of tile t+1 overlaps the dV / dK / dQ UMMAs of tile t.
 template <class Cfg>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
                 const AttnBwdParams p, int* __restrict__ status) {
-  constexpr int D = Cfg::D, KS = Cfg::KS, NKV = Cfg::NKV, NQ = Cfg::NQ, NB = Cfg::NB;
+  constexpr int D = Cfg::D, KS = Cfg::KS, NKV = Cfg::NKV, NQ = Cfg::NQ, NB = Cfg::NB, NCW = Cfg::NCW;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
@@ -160,16 +168,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* kv_full = q_empty + NQ;
   uint64_t* kv_empty = kv_full + NKV;
   uint64_t* misc = kv_empty + NKV;
-  uint64_t* s_full = misc + 0;
-  uint64_t* s_free = misc + 1;
-  uint64_t* dp_full = misc + 2;
-  uint64_t* dp_free = misc + 3;
-  uint64_t* p_ready = misc + 4;
-  uint64_t* p_free = misc + 5;
-  uint64_t* ds_ready = misc + 6;
-  uint64_t* ds_free = misc + 7;
-  uint64_t* dkv_full = misc + 8;
-  uint64_t* dkv_free = misc + 9;
+  uint64_t* sdp_full = misc + 0;   // S and dP of a tile are in TMEM
+  uint64_t* sdp_free = misc + 1;   // ... and have been read by all compute warps
+  uint64_t* pds_ready = misc + 2;  // P and dS of a tile are in shared memory
+  uint64_t* pds_free = misc + 3;   // ... and have been consumed by the dV / dK / dQ UMMAs
+  uint64_t* dkv_full = misc + 4;
+  uint64_t* dkv_free = misc + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::N_BAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx wctx{abort_flag, status};
@@ -180,7 +184,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     for (int s = 0; s < NB; ++s) {
       mbar_init(&b_full[s], 1);
-      mbar_init(&b_empty[s], 8);
+      mbar_init(&b_empty[s], NCW);
     }
     for (int s = 0; s < NQ; ++s) {
       mbar_init(&q_full[s], 1);
@@ -190,16 +194,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 8);
-    mbar_init(dp_full, 1);
-    mbar_init(dp_free, 8);
-    mbar_init(p_ready, 8);
-    mbar_init(p_free, 1);
-    mbar_init(ds_ready, 8);
-    mbar_init(ds_free, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_free, NCW);
+    mbar_init(pds_ready, NCW);
+    mbar_init(pds_free, 1);
     mbar_init(dkv_full, 1);
-    mbar_init(dkv_free, 8);
+    mbar_init(dkv_free, NCW);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -209,7 +209,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tma_prefetch_desc(&tmBias);
     tma_prefetch_desc(&tmMask);
   }
-  if (warp == 9) {
+  if (warp == Cfg::WARP_MMA) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -225,16 +225,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     b = r / p.O;
   };
 
-  if (warp == 8) {
+  if (warp == Cfg::WARP_TMA) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int q_s = 0, kv_s = 0, b_s = 0;
       uint32_t q_ph = 1, kv_ph = 1, b_ph = 1;
       BwdWalk w;
       w.init(blockIdx.x, gridDim.x, p.n_items, p.q_tiles, p.k_tiles, KS, p.n_strips);
+      int b = 0, o = 0, h = 0, cur = -1;
       for (; w.valid(); w.next()) {
-        int b, o, h;
-        decode(w.item, b, o, h);
+        if (w.item != cur) {
+          cur = w.item;
+          decode(cur, b, o, h);
+        }
         if (w.first_kk()) {
           mbar_wait(&q_empty[q_s], q_ph, wctx);
           mbar_expect_tx(&q_full[q_s], 2 * Cfg::TILE);
@@ -267,7 +270,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == Cfg::WARP_MMA) {
     // ------------------------------------------------------------------ UMMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_sd = make_idesc_bf16(128, 128, false, false);  // S, dP
@@ -275,45 +278,44 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, false, true);     // dQ
       constexpr uint32_t swz = swizzle_mode_for_bytes(Cfg::SWZ);
       constexpr uint32_t swz128 = swizzle_mode_for_bytes(128);
+      // Descriptors of stage 0 of every operand; a stage or a k-step only changes the start-address
+      // field (bits 0-13, 16-byte units), so the per-UMMA work is one 64-bit add.
+      const uint64_t dq_k = make_smem_desc(smem_u32(smem + Cfg::OFF_Q), 16, 8 * Cfg::SWZ, swz);     // Q, K-major (S)
+      const uint64_t dk_k = make_smem_desc(smem_u32(smem + Cfg::OFF_K), 16, 8 * Cfg::SWZ, swz);     // K, K-major (S)
+      const uint64_t ddo_k = make_smem_desc(smem_u32(smem + Cfg::OFF_DO), 16, 8 * Cfg::SWZ, swz);   // dO, K-major (dP)
+      const uint64_t dv_k = make_smem_desc(smem_u32(smem + Cfg::OFF_V), 16, 8 * Cfg::SWZ, swz);     // V, K-major (dP)
+      const uint64_t dp_mn = make_smem_desc(smem_u32(smem + Cfg::OFF_P), 16384, 1024, swz128);      // P^T as A (dV)
+      const uint64_t dds_mn = make_smem_desc(smem_u32(smem + Cfg::OFF_DS), 16384, 1024, swz128);    // dS^T as A (dK)
+      const uint64_t dds_k = make_smem_desc(smem_u32(smem + Cfg::OFF_DS), 16, 1024, swz128);        // dS as A (dQ)
+      const uint64_t ddo_mn = make_smem_desc(smem_u32(smem + Cfg::OFF_DO), 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz);  // dO as B (dV)
+      const uint64_t dq_mn = make_smem_desc(smem_u32(smem + Cfg::OFF_Q), 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz);    // Q as B (dK)
+      const uint64_t dk_mn = make_smem_desc(smem_u32(smem + Cfg::OFF_K), 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz);    // K as B (dQ)
+      constexpr uint64_t kTile16 = Cfg::TILE >> 4;
 
       // stage trackers for the "ahead" stream (S, dP) and the "behind" stream (dV, dK, dQ)
       int aq_s = 0, akv_s = 0;
       uint32_t aq_ph = 0, akv_ph = 0;
       int bq_s = 0, bkv_s = 0;
-      uint32_t sfree_ph = 1, dpfree_ph = 1, pready_ph = 0, dsready_ph = 0, dkvfree_ph = 1;
+      uint32_t sdpfree_ph = 1, pdsready_ph = 0, dkvfree_ph = 1;
 
       BwdWalk wa, wb;  // ahead / behind
       wa.init(blockIdx.x, gridDim.x, p.n_items, p.q_tiles, p.k_tiles, KS, p.n_strips);
       wb = wa;
 
-      auto issue_s = [&]() {  // S of tile wa
-        if (wa.first_kk()) {
-          mbar_wait(&q_full[aq_s], aq_ph, wctx);
-        }
+      auto issue_sdp = [&]() {  // S and dP of tile wa, then advance wa
+        if (wa.first_kk()) mbar_wait(&q_full[aq_s], aq_ph, wctx);
         mbar_wait(&kv_full[akv_s], akv_ph, wctx);
-        mbar_wait(s_free, sfree_ph, wctx);
-        sfree_ph ^= 1;
+        mbar_wait(sdp_free, sdpfree_ph, wctx);
+        sdpfree_ph ^= 1;
         tc_fence_after();
-        const uint32_t qa = smem_u32(smem + Cfg::OFF_Q + aq_s * Cfg::TILE);
-        const uint32_t ka = smem_u32(smem + Cfg::OFF_K + akv_s * Cfg::TILE);
+        const uint64_t qo = aq_s * kTile16, ko = akv_s * kTile16;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
-          umma_ss(tmem_base + Cfg::TM_S, make_smem_desc(qa + ks * 32, 16, 8 * Cfg::SWZ, swz),
-                  make_smem_desc(ka + ks * 32, 16, 8 * Cfg::SWZ, swz), idesc_sd, ks != 0);
-        umma_commit(s_full);
-      };
-      auto issue_dp = [&]() {  // dP of tile wa, then advance wa
-        mbar_wait(dp_free, dpfree_ph, wctx);
-        dpfree_ph ^= 1;
-        tc_fence_after();
-        const uint32_t da = smem_u32(smem + Cfg::OFF_DO + aq_s * Cfg::TILE);
-        const uint32_t va = smem_u32(smem + Cfg::OFF_V + akv_s * Cfg::TILE);
+          umma_ss(tmem_base + Cfg::TM_S, dq_k + qo + 2 * ks, dk_k + ko + 2 * ks, idesc_sd, ks != 0);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
-          umma_ss(tmem_base + Cfg::TM_DP, make_smem_desc(da + ks * 32, 16, 8 * Cfg::SWZ, swz),
-                  make_smem_desc(va + ks * 32, 16, 8 * Cfg::SWZ, swz), idesc_sd, ks != 0);
-        umma_commit(dp_full);
-        // advance the ahead stream
+          umma_ss(tmem_base + Cfg::TM_DP, ddo_k + qo + 2 * ks, dv_k + ko + 2 * ks, idesc_sd, ks != 0);
+        umma_commit(sdp_full);
         if (++akv_s == NKV) {
           akv_s = 0;
           akv_ph ^= 1;
@@ -328,50 +330,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       };
 
-      if (wa.valid()) {
-        issue_s();
-        issue_dp();
-      }
+      if (wa.valid()) issue_sdp();
       for (; wb.valid();) {
-        if (wa.valid()) issue_s();  // S of the next tile as soon as the current S sits in registers
-        // ---- dV(kt) (+)= P^T dO
-        mbar_wait(p_ready, pready_ph, wctx);
-        pready_ph ^= 1;
+        // S and dP of the next tile as soon as the current pair has been read out of TMEM
+        if (wa.valid()) issue_sdp();
+        mbar_wait(pds_ready, pdsready_ph, wctx);
+        pdsready_ph ^= 1;
         if (wb.first_qt() && wb.first_kk()) {
           // first accumulation of a strip overwrites dK/dV: the previous strip must have been read out
           mbar_wait(dkv_free, dkvfree_ph, wctx);
           dkvfree_ph ^= 1;
         }
         tc_fence_after();
-        const uint32_t pa = smem_u32(smem + Cfg::OFF_P);
-        const uint32_t dsa = smem_u32(smem + Cfg::OFF_DS);
-        const uint32_t qa = smem_u32(smem + Cfg::OFF_Q + bq_s * Cfg::TILE);
-        const uint32_t doa = smem_u32(smem + Cfg::OFF_DO + bq_s * Cfg::TILE);
-        const uint32_t ka = smem_u32(smem + Cfg::OFF_K + bkv_s * Cfg::TILE);
+        const uint64_t qo = bq_s * kTile16, ko = bkv_s * kTile16;
         const uint32_t acc_kv = wb.first_qt() ? 0u : 1u;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)  // 16 queries per step
-          umma_ss(tmem_base + Cfg::TM_DV + wb.kk * D, make_smem_desc(pa + ks * 2048, 16384, 1024, swz128),
-                  make_smem_desc(doa + ks * 16 * Cfg::SWZ, 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz), idesc_kv,
-                  (ks != 0) ? 1u : acc_kv);
-        umma_commit(p_free);
-        if (wa.valid()) issue_dp();  // dP of the next tile
-        // ---- dK(kt) (+)= dS^T Q ; dQ(qt) (+)= dS K
-        mbar_wait(ds_ready, dsready_ph, wctx);
-        dsready_ph ^= 1;
-        tc_fence_after();
+        // dV(kt) (+)= P^T dO ; dK(kt) (+)= dS^T Q   (16 queries per step)
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tmem_base + Cfg::TM_DK + wb.kk * D, make_smem_desc(dsa + ks * 2048, 16384, 1024, swz128),
-                  make_smem_desc(qa + ks * 16 * Cfg::SWZ, 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz), idesc_kv,
-                  (ks != 0) ? 1u : acc_kv);
+          umma_ss(tmem_base + Cfg::TM_DV + wb.kk * D, dp_mn + (uint64_t)(ks * 128), ddo_mn + qo + (uint64_t)(ks * Cfg::SWZ),
+                  idesc_kv, (ks != 0) ? 1u : acc_kv);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ss(tmem_base + Cfg::TM_DK + wb.kk * D, dds_mn + (uint64_t)(ks * 128), dq_mn + qo + (uint64_t)(ks * Cfg::SWZ),
+                  idesc_kv, (ks != 0) ? 1u : acc_kv);
+        // dQ(qt) (+)= dS K   (16 keys per step)
         const uint32_t acc_q = wb.first_kk() ? 0u : 1u;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)  // 16 keys per step
-          umma_ss(tmem_base + Cfg::TM_DQ, make_smem_desc(dsa + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, swz128),
-                  make_smem_desc(ka + ks * 16 * Cfg::SWZ, 128 * Cfg::SWZ, 8 * Cfg::SWZ, swz), idesc_dq,
-                  (ks != 0) ? 1u : acc_q);
-        umma_commit(ds_free);
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ss(tmem_base + Cfg::TM_DQ, dds_k + (uint64_t)((ks >> 2) * 1024 + (ks & 3) * 2),
+                  dk_mn + ko + (uint64_t)(ks * Cfg::SWZ), idesc_dq, (ks != 0) ? 1u : acc_q);
+        umma_commit(pds_free);
         umma_commit(&kv_empty[bkv_s]);
         if (++bkv_s == NKV) bkv_s = 0;
         const bool last_kk = wb.last_kk();
@@ -385,63 +373,79 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    // ------------------------------------------------------------------ compute warps (2 threads per query row)
-    const int hf = warp >> 2;                   // which 64-key half of the tile
+    // ------------------------------------------------------------------ compute warps
+    const int part = warp >> 2;                 // which 32-key slice of the tile
     const int row = 32 * (warp & 3) + lane;     // query row in the tile == TMEM lane
     const uint32_t lane_base = 32 * (warp & 3);
-    const uint32_t t_s = tmem_addr(tmem_base, lane_base, Cfg::TM_S + 64 * hf);
-    const uint32_t t_dp = tmem_addr(tmem_base, lane_base, Cfg::TM_DP + 64 * hf);
-    constexpr int DH = D / 2;                   // output columns per thread
-    const uint32_t t_dq = tmem_addr(tmem_base, lane_base, Cfg::TM_DQ + DH * hf);
-    uint8_t* p_row = smem + Cfg::OFF_P + hf * 16384 + row * 128;
-    uint8_t* ds_row = smem + Cfg::OFF_DS + hf * 16384 + row * 128;
+    const uint32_t t_s = tmem_addr(tmem_base, lane_base, Cfg::TM_S + 32 * part);
+    const uint32_t t_dp = tmem_addr(tmem_base, lane_base, Cfg::TM_DP + 32 * part);
+    constexpr int DQ = D / 4;                   // output columns per thread
+    const uint32_t t_dq = tmem_addr(tmem_base, lane_base, Cfg::TM_DQ + DQ * part);
+    // the thread's 32 keys are four 16-byte pieces of a 128-byte row of one 64-key half tile
+    const int half_off = (part >> 1) * 16384 + row * 128;
+    const int piece0 = (part & 1) * 4;
     constexpr float kLog2e = 1.4426950408889634f;
     const float scale = p.scale;
+    const uint64_t scale2 = f2_pack(scale, scale);
+    const uint64_t log2e2 = f2_pack(kLog2e, kLog2e);
 
-    uint32_t sfull_ph = 0, dpfull_ph = 0, pfree_ph = 1, dsfree_ph = 1, kv_ph = 0, b_ph = 0, dkvfull_ph = 0;
+    uint32_t sdpfull_ph = 0, pdsfree_ph = 1, kv_ph = 0, b_ph = 0, dkvfull_ph = 0;
     int kv_s = 0, b_s = 0;
     float neg_lse2 = -INFINITY, delta = 0.f;
     bool have_prev_dq = false;  // a finished dQ tile waits in TMEM
     int prev_q0 = 0, prev_b = 0, prev_o = 0, prev_h = 0, prev_strip = 0;
 
-    // read a finished dQ tile out of TMEM and store it (or fold it into the per-CTA running sum)
-    auto flush_dq = [&](int b, int o, int h, int q0, int strip) {
-      const int q = q0 + row;
-      float v[DH];
-#pragma unroll
-      for (int c = 0; c < DH; c += 8) {
-        uint32_t r8[8];
-        tmem_ld8(t_dq + c, r8);
+    // read DQ consecutive accumulator columns of this thread's row
+    auto ld_cols = [&](uint32_t taddr, float (&v)[DQ]) {
+      if constexpr (DQ == 4) {
+        uint32_t r[4];
+        tmem_ld4(taddr, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[c + i] = __uint_as_float(r8[i]);
+        for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < DQ; c += 8) {
+          uint32_t r[8];
+          tmem_ld8(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[c + i] = __uint_as_float(r[i]);
+        }
       }
+    };
+    auto st_cols = [&](__nv_bfloat16* dst, const float (&v)[DQ], float mul) {
+      if constexpr (DQ == 4) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(v[0] * mul, v[1] * mul), pack_bf16x2(v[2] * mul, v[3] * mul));
+      } else {
+#pragma unroll
+        for (int c = 0; c < DQ; c += 8)
+          *reinterpret_cast<uint4*>(dst + c) =
+              make_uint4(pack_bf16x2(v[c] * mul, v[c + 1] * mul), pack_bf16x2(v[c + 2] * mul, v[c + 3] * mul),
+                         pack_bf16x2(v[c + 4] * mul, v[c + 5] * mul), pack_bf16x2(v[c + 6] * mul, v[c + 7] * mul));
+      }
+    };
+
+    // store a finished dQ tile that has been read out of TMEM (or fold it into the per-CTA running sum)
+    auto store_dq = [&](int b, int o, int h, int q0, int strip, float (&v)[DQ]) {
+      const int q = q0 + row;
       if (q >= p.N) return;
       if (p.n_strips > 1) {
-        float* sc = p.dq_scratch + ((int64_t)blockIdx.x * p.N + q) * D + DH * hf;
+        float* sc = p.dq_scratch + ((int64_t)blockIdx.x * p.N + q) * D + DQ * part;
         if (strip > 0) {
 #pragma unroll
-          for (int c = 0; c < DH; c += 4) {
+          for (int c = 0; c < DQ; c += 4) {
             const float4 o4 = *reinterpret_cast<const float4*>(sc + c);
             v[c] += o4.x; v[c + 1] += o4.y; v[c + 2] += o4.z; v[c + 3] += o4.w;
           }
         }
         if (strip + 1 < p.n_strips) {
 #pragma unroll
-          for (int c = 0; c < DH; c += 4) *reinterpret_cast<float4*>(sc + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+          for (int c = 0; c < DQ; c += 4) *reinterpret_cast<float4*>(sc + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
           return;
         }
       }
-      __nv_bfloat16* dst = p.dq + ((((int64_t)b * p.O + o) * p.H + h) * p.N + q) * D + DH * hf;
-#pragma unroll
-      for (int c = 0; c < DH; c += 8) {
-        uint4 pk;
-        pk.x = pack_bf16x2(v[c + 0] * scale, v[c + 1] * scale);
-        pk.y = pack_bf16x2(v[c + 2] * scale, v[c + 3] * scale);
-        pk.z = pack_bf16x2(v[c + 4] * scale, v[c + 5] * scale);
-        pk.w = pack_bf16x2(v[c + 6] * scale, v[c + 7] * scale);
-        *reinterpret_cast<uint4*>(dst + c) = pk;
-      }
+      st_cols(p.dq + ((((int64_t)b * p.O + o) * p.H + h) * p.N + q) * D + DQ * part, v, scale);
     };
 
     // lse / delta of this thread's query row, loaded one query tile ahead of their first use
@@ -455,8 +459,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int pq = t.qt * 128 + row;
         if (pq < p.N) {
           const int64_t idx = (((int64_t)pb * p.O + po) * p.H + phh) * p.N + pq;
-          l_pref = p.lse[idx];
-          d_pref = p.delta[idx];
+          l_pref = __ldg(p.lse + idx);
+          d_pref = __ldg(p.delta + idx);
         }
       }
     };
@@ -464,10 +468,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     BwdWalk w;
     w.init(blockIdx.x, gridDim.x, p.n_items, p.q_tiles, p.k_tiles, KS, p.n_strips);
     prefetch_row_scalars(w);
+    int b = 0, o = 0, h = 0, cur = -1;
     for (; w.valid(); w.next()) {
-      int b, o, h;
-      decode(w.item, b, o, h);
-      const int q = w.qt * 128 + row;
+      if (w.item != cur) {
+        cur = w.item;
+        decode(cur, b, o, h);
+      }
       const int kt = w.kt();
       if (w.first_kk()) {
         // values fetched one query tile ahead; fetch the next tile's now
@@ -478,58 +484,67 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int t = 0; t < sl; ++t) nx.next();
         prefetch_row_scalars(nx);
       }
+      const uint64_t nlse2 = f2_pack(neg_lse2, neg_lse2);
+      const uint64_t ndel2 = f2_pack(-delta, -delta);
 
-      // ---------------- phase 1: P = exp(S - lse)
-      mbar_wait(s_full, sfull_ph, wctx);
-      sfull_ph ^= 1;
+      mbar_wait(sdp_full, sdpfull_ph, wctx);
+      sdpfull_ph ^= 1;
       mbar_wait(&kv_full[kv_s], kv_ph, wctx);
       mbar_wait(&b_full[b_s], b_ph, wctx);
       tc_fence_after();
-      const uint8_t* bias_row = smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE + hf * 16384 + row * 128;
-      const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_MASK + kv_s * 512) + 64 * hf;
+      const uint8_t* bias_row = smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE + half_off;
+      const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_MASK + kv_s * 512) + 32 * part;
       const bool tail = (kt + 1) * 128 > p.N;
-      float pf[64];
-      uint32_t ppk[32];
-      {
-        uint32_t(*r32)[32] = reinterpret_cast<uint32_t(*)[32]>(pf);
-        tmem_ld32(t_s, r32[0]);
-        tmem_ld32(t_s + 32, r32[1]);
+      const bool general = tail || __any_sync(0xffffffffu, mask_row[lane] != 0.f);
+
+      uint32_t ppk[16], dpk[16];  // bf16 pairs of P and dS of this thread's 32 keys
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {  // 16 keys per step
+        uint32_t rs[16], rd[16];
+        tmem_ld16(t_s + 16 * ch, rs);
+        tmem_ld16(t_dp + 16 * ch, rd);
+        const uint4 bv0 = *reinterpret_cast<const uint4*>(bias_row + (((piece0 + 2 * ch) ^ (row & 7)) << 4));
+        const uint4 bv1 = *reinterpret_cast<const uint4*>(bias_row + (((piece0 + 2 * ch + 1) ^ (row & 7)) << 4));
         tmem_ld_wait();
-      }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint32_t* raw = reinterpret_cast<const uint32_t*>(pf) + 16 * c;
-        uint4 bv[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) bv[u] = *reinterpret_cast<const uint4*>(bias_row + (((2 * c + u) ^ (row & 7)) << 4));
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const uint32_t bw[4] = {bv[u].x, bv[u].y, bv[u].z, bv[u].w};
-          const float4 mk0 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u);
-          const float4 mk1 = *reinterpret_cast<const float4*>(mask_row + 16 * c + 8 * u + 4);
-          const float mk[8] = {mk0.x, mk0.y, mk0.z, mk0.w, mk1.x, mk1.y, mk1.z, mk1.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i0 = 8 * u + 2 * e;
-            float v0 = fmaf(__uint_as_float(raw[i0]), scale, __uint_as_float(bw[e] << 16)) + mk[2 * e];
-            float v1 = fmaf(__uint_as_float(raw[i0 + 1]), scale, __uint_as_float(bw[e] & 0xFFFF0000u)) + mk[2 * e + 1];
-            if (tail) {
-              if (kt * 128 + 64 * hf + 16 * c + i0 >= p.N) v0 = -INFINITY;
-              if (kt * 128 + 64 * hf + 16 * c + i0 + 1 >= p.N) v1 = -INFINITY;
-            }
-            const float p0 = ex2_approx(fmaf(v0, kLog2e, neg_lse2));
-            const float p1 = ex2_approx(fmaf(v1, kLog2e, neg_lse2));
-            pf[16 * c + i0] = p0;
-            pf[16 * c + i0 + 1] = p1;
-            ppk[8 * c + 4 * u + e] = pack_bf16x2(p0, p1);
+        if (ch == 1) {
+          // S, dP and the bias tile have been read: the next pair of UMMAs / the next bias load may overwrite them
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(sdp_free);
+            mbar_arrive(&b_empty[b_s]);
           }
         }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_free);
-        mbar_arrive(&b_empty[b_s]);
+        const uint32_t bw[8] = {bv0.x, bv0.y, bv0.z, bv0.w, bv1.x, bv1.y, bv1.z, bv1.w};
+        uint64_t vv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          vv[e] = f2_fma(f2_pack_bits(rs[2 * e], rs[2 * e + 1]), scale2, f2_pack_bits(bw[e] << 16, bw[e] & 0xFFFF0000u));
+        if (general) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 mk = *reinterpret_cast<const float2*>(mask_row + 16 * ch + 2 * e);
+            float v0, v1;
+            f2_unpack(f2_add(vv[e], f2_pack(mk.x, mk.y)), v0, v1);
+            if (tail) {
+              const int k0 = kt * 128 + 32 * part + 16 * ch + 2 * e;
+              if (k0 >= p.N) v0 = -INFINITY;
+              if (k0 + 1 >= p.N) v1 = -INFINITY;
+            }
+            vv[e] = f2_pack(v0, v1);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const uint64_t v2 = vv[e];
+          float a0, a1;
+          f2_unpack(f2_fma(v2, log2e2, nlse2), a0, a1);
+          const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
+          float d0, d1;
+          f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(rd[2 * e], rd[2 * e + 1]), ndel2)), d0, d1);
+          ppk[8 * ch + e] = pack_bf16x2(p0, p1);
+          dpk[8 * ch + e] = pack_bf16x2(d0, d1);
+        }
       }
       if (++b_s == NB) {
         b_s = 0;
@@ -539,59 +554,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         kv_s = 0;
         kv_ph ^= 1;
       }
-      // P tile -> smem (the dV UMMA of the previous tile has long finished)
-      mbar_wait(p_free, pfree_ph, wctx);
-      pfree_ph ^= 1;
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        *reinterpret_cast<uint4*>(p_row + ((u ^ (row & 7)) << 4)) =
-            make_uint4(ppk[4 * u], ppk[4 * u + 1], ppk[4 * u + 2], ppk[4 * u + 3]);
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
 
-      // ---------------- phase 2: dS = P (dP - delta)
-      mbar_wait(dp_full, dpfull_ph, wctx);
-      dpfull_ph ^= 1;
+      // the dV / dK / dQ UMMAs of the previous tile are done: the P and dS tiles are free and a finished dQ can be read
+      mbar_wait(pds_free, pdsfree_ph, wctx);
+      pdsfree_ph ^= 1;
       tc_fence_after();
-      uint32_t dpk[32];
-      uint32_t rdp[64];
-      {
-        uint32_t(*r32)[32] = reinterpret_cast<uint32_t(*)[32]>(rdp);
-        tmem_ld32(t_dp, r32[0]);
-        tmem_ld32(t_dp + 32, r32[1]);
-        tmem_ld_wait();
-      }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint32_t* raw = rdp + 16 * c;
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const float d0 = pf[16 * c + i] * (__uint_as_float(raw[i]) - delta);
-          const float d1 = pf[16 * c + i + 1] * (__uint_as_float(raw[i + 1]) - delta);
-          dpk[8 * c + (i >> 1)] = pack_bf16x2(d0, d1);
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dp_free);
-
-      // the dK/dQ UMMAs of the previous tile are done: dS smem is free and a finished dQ can be read
-      mbar_wait(ds_free, dsfree_ph, wctx);
-      dsfree_ph ^= 1;
-      tc_fence_after();
-      if (have_prev_dq) {
-        flush_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip);
+      float dqv[DQ];
+      const bool store_prev = have_prev_dq;
+      if (store_prev) {
+        ld_cols(t_dq, dqv);
         have_prev_dq = false;
         tc_fence_before();
       }
+      {
+        uint8_t* p_row = smem + Cfg::OFF_P + half_off;
+        uint8_t* ds_row = smem + Cfg::OFF_DS + half_off;
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        *reinterpret_cast<uint4*>(ds_row + ((u ^ (row & 7)) << 4)) =
-            make_uint4(dpk[4 * u], dpk[4 * u + 1], dpk[4 * u + 2], dpk[4 * u + 3]);
+        for (int u = 0; u < 4; ++u) {
+          const int off = ((piece0 + u) ^ (row & 7)) << 4;
+          *reinterpret_cast<uint4*>(p_row + off) = make_uint4(ppk[4 * u], ppk[4 * u + 1], ppk[4 * u + 2], ppk[4 * u + 3]);
+          *reinterpret_cast<uint4*>(ds_row + off) = make_uint4(dpk[4 * u], dpk[4 * u + 1], dpk[4 * u + 2], dpk[4 * u + 3]);
+        }
+      }
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_ready);
+      if (lane == 0) mbar_arrive(pds_ready);
+      if (store_prev) store_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip, dqv);
 
       if (w.last_kk()) {
         have_prev_dq = true;
@@ -603,43 +591,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_wait(dkv_full, dkvfull_ph, wctx);
         dkvfull_ph ^= 1;
         tc_fence_after();
-        flush_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip);
+        ld_cols(t_dq, dqv);
         have_prev_dq = false;
-        const int nk = w.strip_len();
-        for (int kk = 0; kk < nk; ++kk) {
-          const int key = (w.strip * KS + kk) * 128 + row;
-          const int64_t base = ((((int64_t)b * p.O + o) * p.H + h) * p.N + key) * D + DH * hf;
-#pragma unroll
-          for (int which = 0; which < 2; ++which) {
-            const uint32_t t_src = tmem_addr(tmem_base, lane_base, (which ? Cfg::TM_DV : Cfg::TM_DK) + kk * D + DH * hf);
-            const float mul = which ? 1.f : scale;
-            __nv_bfloat16* dst = (which ? p.dv : p.dk) + base;
-#pragma unroll
-            for (int c = 0; c < DH; c += 8) {
-              uint32_t r8[8];
-              tmem_ld8(t_src + c, r8);
-              tmem_ld_wait();
-              if (key < p.N) {
-                uint4 pk;
-                pk.x = pack_bf16x2(__uint_as_float(r8[0]) * mul, __uint_as_float(r8[1]) * mul);
-                pk.y = pack_bf16x2(__uint_as_float(r8[2]) * mul, __uint_as_float(r8[3]) * mul);
-                pk.z = pack_bf16x2(__uint_as_float(r8[4]) * mul, __uint_as_float(r8[5]) * mul);
-                pk.w = pack_bf16x2(__uint_as_float(r8[6]) * mul, __uint_as_float(r8[7]) * mul);
-                *reinterpret_cast<uint4*>(dst + c) = pk;
-              }
+        store_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip, dqv);
+        {
+          const int nk = w.strip_len();
+          for (int kk = 0; kk < nk; ++kk) {
+            const int key = (w.strip * KS + kk) * 128 + row;
+            const int64_t base = ((((int64_t)b * p.O + o) * p.H + h) * p.N + key) * D + DQ * part;
+            float vk1[DQ], vv1[DQ];
+            ld_cols(tmem_addr(tmem_base, lane_base, Cfg::TM_DK + kk * D + DQ * part), vk1);
+            ld_cols(tmem_addr(tmem_base, lane_base, Cfg::TM_DV + kk * D + DQ * part), vv1);
+            if (key < p.N) {
+              st_cols(p.dk + base, vk1, scale);
+              st_cols(p.dv + base, vv1, 1.f);
             }
           }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dkv_free);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(dkv_free);
       }
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == Cfg::WARP_MMA) {
     __syncwarp();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
@@ -876,11 +854,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_after();
       const float* mask_row =
           reinterpret_cast<const float*>(smem + Cfg::OFF_ST + s * Cfg::STAGE + 4 * Cfg::TILE) + CPT * part;
-#ifdef TPF_DB_NOGENERAL
-      const bool general = false;
-#else
       const bool general = tail || __any_sync(0xffffffffu, mask_row[lane] != 0.f);
-#endif
       const uint32_t t_s = tmem_addr(tmem_base, lane_base, buf * 256 + CPT * part);
       const uint32_t t_dp = tmem_addr(tmem_base, lane_base, buf * 256 + 128 + CPT * part);
       // 8 columns per step; the TMEM loads of step c+1 are in flight while step c is computed
@@ -992,7 +966,7 @@ int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
   auto kern = attn_bwd_kernel<Cfg>;
   static PerDeviceOnce once;  // per instantiation
   if (int rc = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, once)) return rc;
-  kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }
