@@ -495,7 +495,10 @@ def block_ms(n, rank, world, group, dev, steps=5, warmup=3):
 
 
 def run_gpu(args, rank, world, local_rank):
+    import faulthandler
     import torch.distributed as dist
+    # a stuck phase ends the run with every thread's stack on stderr instead of waiting for the caller's limit
+    faulthandler.dump_traceback_later(args.watchdog, exit=True)
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     group = None
@@ -506,7 +509,10 @@ def run_gpu(args, rank, world, local_rank):
         log(rank, f"init_process_group nccl world={world}")
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=PG_TIMEOUT_S))
         group = dist.group.WORLD
-    barrier = (lambda: dist.barrier()) if world > 1 else None
+        # host-side rendezvous (barriers around timed regions, the max over ranks of the timings) goes
+        # through gloo, so that no eager NCCL collective has to follow the replay of the captured step
+        host_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=PG_TIMEOUT_S))
+    barrier = (lambda: dist.barrier(group=host_group)) if world > 1 else None
     from openfold3_triangle_kernel_b200 import _cabi as C
     C.load()
     log(rank, "building workload")
@@ -518,13 +524,6 @@ def run_gpu(args, rank, world, local_rank):
     torch.cuda.synchronize()
     if C.device_status() != 0:
         raise RuntimeError("device status word is non-zero after warm-up (a bounded wait timed out)")
-
-    log(rank, f"timed region: {args.steps} steps")
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    launches0 = C.load().tpf_launch_count()
-    sec = _time_loop(wl.step, args.steps, barrier)
-    launches = C.load().tpf_launch_count() - launches0
-    clocks = sampler.stop() if sampler else None
 
     # per-stage times (same buffers, CUDA events on the launching stream)
     log(rank, "stage timers")
@@ -540,8 +539,16 @@ def run_gpu(args, rank, world, local_rank):
                    ("trimul_out_bwd_outproj", lambda: wl.trimul_bwd(0, 1)), ("trimul_out_bwd_contract", lambda: wl.trimul_bwd(0, 2)),
                    ("trimul_out_bwd_proj", lambda: wl.trimul_bwd(0, 4))]
     else:
+        # the collectives of the sharded step on their own (same shapes and dtypes as inside the step)
+        ab = [torch.empty(1, TRI["C"], wl.Nl, TRI["N"], device=dev, dtype=torch.bfloat16) for _ in range(2)]
+        xc = torch.empty(1, TRI["C"] // world, TRI["N"], TRI["N"], device=dev, dtype=torch.bfloat16)
+        wflat = torch.empty(6 * TRI["C"] * TRI["C"] + 4 * TRI["C"], device=dev)
         stages += [("trimul_out_fwd_bwd_sharded", lambda: wl.trimul_sharded(0)),
-                   ("trimul_in_fwd_bwd_sharded", lambda: wl.trimul_sharded(1))]
+                   ("trimul_in_fwd_bwd_sharded", lambda: wl.trimul_sharded(1)),
+                   ("coll_all_to_all_a_b_rows_to_channels", lambda: wl.dap.rows_to_channels_many(ab, group)),
+                   ("coll_all_to_all_x_channels_to_rows", lambda: wl.dap.channels_to_rows(xc, group)),
+                   ("coll_all_reduce_dbias_fp32", lambda: dist.all_reduce(wl.dbias, group=group)),
+                   ("coll_all_reduce_weight_grads", lambda: dist.all_reduce(wflat, group=group))]
     for name, fn in stages:
         fn()
         stage[name] = _time_loop(fn, n_st, barrier) / n_st * 1e6  # us
@@ -563,14 +570,6 @@ def run_gpu(args, rank, world, local_rank):
     e2e_sec = max(e0.elapsed_time(e1) / 1e3, time.perf_counter() - t0) / n_e2e
     status = C.device_status()
 
-    t_step = torch.tensor([sec / args.steps, e2e_sec] + [stage[k] for k in sorted(stage)], device=dev,
-                          dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t_step, op=dist.ReduceOp.MAX)
-    vals = [float(x) for x in t_step.tolist()]
-    step_sec, e2e_sec = vals[0], vals[1]
-    stage = dict(zip(sorted(stage), vals[2:]))
-
     parity = None
     if world > 1:
         log(rank, "dap parity (not timed)")
@@ -583,6 +582,42 @@ def run_gpu(args, rank, world, local_rank):
                 ms, fl = block_ms(n, rank, world, group, dev)
                 blocks[n] = (ms, fl)
     status |= C.device_status()
+
+    # The sharded step is many small launches (per-rank kernels shrink with N, collectives sit between
+    # them), so at N > 1 the host cannot keep the stream fed: the whole step - kernels and NCCL
+    # collectives - is captured once in a CUDA graph and replayed.  N = 1 launches directly.
+    step_fn, graphed = wl.step, False
+    launches_per_step = None
+    if world > 1 and not args.no_graph:
+        log(rank, "capturing the sharded step in a CUDA graph")
+        torch.cuda.synchronize()
+        barrier()
+        l0 = C.load().tpf_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            wl.step()
+        launches_per_step = C.load().tpf_launch_count() - l0
+        step_fn, graphed = graph.replay, True
+        for _ in range(3):
+            step_fn()
+        torch.cuda.synchronize()
+
+    log(rank, f"timed region: {args.steps} steps")
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = C.load().tpf_launch_count()
+    sec = _time_loop(step_fn, args.steps, barrier)
+    launches = C.load().tpf_launch_count() - launches0
+    if graphed:
+        launches = launches_per_step * args.steps   # replayed launches do not pass through the library's counter
+    clocks = sampler.stop() if sampler else None
+
+    status |= C.device_status()
+    t_step = torch.tensor([sec / args.steps, e2e_sec] + [stage[k] for k in sorted(stage)], dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_step, op=dist.ReduceOp.MAX, group=host_group)
+    vals = [float(x) for x in t_step.tolist()]
+    step_sec, e2e_sec = vals[0], vals[1]
+    stage = dict(zip(sorted(stage), vals[2:]))
 
     if rank == 0:
         peaks = _peaks()
@@ -626,6 +661,8 @@ def run_gpu(args, rank, world, local_rank):
                         parallelism=("single GPU" if world == 1 else
                                      f"axial x{world}: attention outer rows sharded + dBias all-reduce; TriMul pair rows "
                                      f"sharded, all-to-all to channel shards for the k-contraction and back"),
+                        launch=("CUDA graph replay of the whole sharded step (kernels + NCCL collectives)" if graphed
+                                else "direct launches"),
                         l2_policy="working set per step (>1 GB over all ranks) exceeds the 126 MB L2; inputs are "
                                   "re-read from HBM every step",
                         seeds=dict(attention=2, trimul=3)),
@@ -649,8 +686,17 @@ def run_gpu(args, rank, world, local_rank):
             line[f"block_n{n}_tflops"] = fl / (ms * 1e-3) / 1e12
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
+        barrier()
+        faulthandler.cancel_dump_traceback_later()
+        if graphed:
+            # Tearing down an NCCL communicator whose collectives sit in an instantiated CUDA graph did not
+            # return on this stack (NCCL 2.28 / torch 2.11): every rank has passed the barrier and rank 0 has
+            # printed its line, so leave without the teardown.
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         dist.destroy_process_group()
+    faulthandler.cancel_dump_traceback_later()
 
 
 def main():
@@ -661,6 +707,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-block", action="store_true", help="do not time the N=768 / N=1536 pair-stack block")
     ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU oracle beside the GPU run")
+    ap.add_argument("--watchdog", type=int, default=900, help="seconds after which a hung run dumps its stacks and exits")
+    ap.add_argument("--no-graph", action="store_true", help="N > 1: launch the sharded step directly instead of replaying a CUDA graph")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

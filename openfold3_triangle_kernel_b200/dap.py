@@ -114,10 +114,14 @@ def axial_attention(q, k, v, pair_bias, res_mask=None, group=None, attention_fn=
     """``q, k, v``: this rank's outer rows ``[*B, O/P, H, N, D]``; ``res_mask`` likewise
     ``[*B, O/P, 1, 1, N]``; ``pair_bias`` replicated ``[*B, 1, H, N, N]``.  Returns the local
     ``[*B, O/P, N, H, D]``.  The bias gradient every rank receives is the full sum over all
-    outer rows (fp32 all-reduce when the bias is fp32, else in the bias dtype)."""
+    outer rows, all-reduced in fp32."""
     if attention_fn is None:
         from .attention import turbo_attention as attention_fn
-    bias = _SumGradOverRanks.apply(pair_bias, group)
+    # The operator returns the bias gradient in the bias dtype.  Handing it an fp32 copy of the bias (the
+    # kernels round it back to the same bf16 values) keeps each rank's partial sum in fp32 through the
+    # all-reduce; the single cast to the caller's dtype happens after the sum.
+    wide = pair_bias if pair_bias.dtype in (torch.float32, torch.float64) else pair_bias.float()
+    bias = _SumGradOverRanks.apply(wide, group)
     return attention_fn(q, k, v, pair_bias=bias, res_mask=res_mask)
 
 
