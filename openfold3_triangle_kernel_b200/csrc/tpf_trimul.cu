@@ -138,12 +138,17 @@ __global__ void __launch_bounds__(256) trimul_xnorm_fwd_kernel(const bf16* __res
                                                                const float* __restrict__ beta, bf16* __restrict__ xln,
                                                                float* __restrict__ mean, float* __restrict__ rstd,
                                                                int64_t NN, int tiles_per_batch) {
-  __shared__ float tile[C][65];
+  // 32 rows per CTA: small tiles keep a dozen CTAs per SM in flight, which is what hides the
+  // load -> transpose -> reduce -> store chain of each of them
+  constexpr int TR = 32;
+  constexpr int RPW = TR / 8;  // rows per warp, handled together so that their reductions overlap
+  __shared__ float tile[C][TR + 1];
   const int bb = blockIdx.x / tiles_per_batch;
-  const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * 64;
+  const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * TR;
   // 16-byte loads: 8 consecutive rows of one channel (NN is a multiple of 8)
-  for (int idx = threadIdx.x; idx < C * 8; idx += 256) {
-    const int c = idx >> 3, j8 = idx & 7;
+#pragma unroll
+  for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
+    const int c = idx / (TR / 8), j8 = idx % (TR / 8);
     uint4 u = make_uint4(0u, 0u, 0u, 0u);
     if (r0 + 8 * j8 < NN) u = *reinterpret_cast<const uint4*>(x_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8);
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -155,34 +160,58 @@ __global__ void __launch_bounds__(256) trimul_xnorm_fwd_kernel(const bf16* __res
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int j = warp; j < 64; j += 8) {
-    float s1 = 0.f, s2 = 0.f;
+  constexpr int CPL = C / 32;  // channels per lane: lane, lane + 32, ...
+  float v[RPW][CPL], s1[RPW], s2[RPW];
 #pragma unroll
-    for (int c = 2 * lane; c < C; c += 64) {
-      const float v0 = tile[c][j], v1 = tile[c + 1][j];
-      s1 += v0 + v1;
-      s2 += v0 * v0 + v1 * v1;
-    }
+  for (int r = 0; r < RPW; ++r) {
+    const int j = warp * RPW + r;
+    s1[r] = 0.f;
+    s2[r] = 0.f;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      s1 += __shfl_xor_sync(0xffffffffu, s1, off);
-      s2 += __shfl_xor_sync(0xffffffffu, s2, off);
+    for (int k = 0; k < CPL; ++k) {
+      v[r][k] = tile[lane + 32 * k][j];
+      s1[r] += v[r][k];
+      s2[r] += v[r][k] * v[r][k];
     }
-    const float mu = s1 * (1.f / C);
-    const float rs = rsqrtf(fmaxf(s2 * (1.f / C) - mu * mu, 0.f) + 1e-5f);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      s1[r] += __shfl_xor_sync(0xffffffffu, s1[r], off);
+      s2[r] += __shfl_xor_sync(0xffffffffu, s2[r], off);
+    }
+  }
+  float g[CPL], bt[CPL];
+#pragma unroll
+  for (int k = 0; k < CPL; ++k) {
+    g[k] = gamma[lane + 32 * k];
+    bt[k] = beta[lane + 32 * k];
+  }
+  __syncthreads();  // every warp has read its rows: the tile is reused for the normalised values
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    const int j = warp * RPW + r;
+    const float mu = s1[r] * (1.f / C);
+    const float rs = rsqrtf(fmaxf(s2[r] * (1.f / C) - mu * mu, 0.f) + 1e-5f);
+#pragma unroll
+    for (int k = 0; k < CPL; ++k) tile[lane + 32 * k][j] = (v[r][k] - mu) * rs * g[k] + bt[k];
+    if (lane == 0 && r0 + j < NN) {
+      mean[(int64_t)bb * NN + r0 + j] = mu;
+      rstd[(int64_t)bb * NN + r0 + j] = rs;
+    }
+  }
+  __syncthreads();
+  // row-major stores: 16 bytes (8 channels) per thread, a warp covers two whole rows
+  for (int idx = threadIdx.x; idx < TR * (C / 8); idx += 256) {
+    const int j = idx / (C / 8), c8 = idx % (C / 8);
     if (r0 + j < NN) {
-      const int64_t row = (int64_t)bb * NN + r0 + j;
-#pragma unroll
-      for (int c = 2 * lane; c < C; c += 64) {
-        const float2 g = *reinterpret_cast<const float2*>(gamma + c);
-        const float2 b = *reinterpret_cast<const float2*>(beta + c);
-        *reinterpret_cast<uint32_t*>(xln + row * C + c) =
-            pack_bf16x2((tile[c][j] - mu) * rs * g.x + b.x, (tile[c + 1][j] - mu) * rs * g.y + b.y);
-      }
-      if (lane == 0) {
-        mean[row] = mu;
-        rstd[row] = rs;
-      }
+      uint4 o;
+      o.x = pack_bf16x2(tile[8 * c8 + 0][j], tile[8 * c8 + 1][j]);
+      o.y = pack_bf16x2(tile[8 * c8 + 2][j], tile[8 * c8 + 3][j]);
+      o.z = pack_bf16x2(tile[8 * c8 + 4][j], tile[8 * c8 + 5][j]);
+      o.w = pack_bf16x2(tile[8 * c8 + 6][j], tile[8 * c8 + 7][j]);
+      *reinterpret_cast<uint4*>(xln + ((int64_t)bb * NN + r0 + j) * C + 8 * c8) = o;
     }
   }
 }
@@ -451,22 +480,40 @@ __global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __res
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int j = warp; j < TR; j += 8) {
-    float a1 = 0.f, a2 = 0.f;
+  {
+    // the four rows of a warp are reduced together so that their shuffle chains overlap
+    constexpr int RPW = TR / 8;
+    float a1[RPW], a2[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      a1[r] = 0.f;
+      a2[r] = 0.f;
+    }
 #pragma unroll
     for (int c = lane; c < C; c += 32) {
-      const float g = gamma[c] * dg[c][j];
-      a1 += g;
-      a2 += g * xh[c][j];
+      const float gm = gamma[c];
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const int j = warp * RPW + r;
+        const float g = gm * dg[c][j];
+        a1[r] += g;
+        a2[r] += g * xh[c][j];
+      }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
-      a1 += __shfl_xor_sync(0xffffffffu, a1, off);
-      a2 += __shfl_xor_sync(0xffffffffu, a2, off);
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        a1[r] += __shfl_xor_sync(0xffffffffu, a1[r], off);
+        a2[r] += __shfl_xor_sync(0xffffffffu, a2[r], off);
+      }
     }
     if (lane == 0) {
-      s_m1[j] = a1 * (1.f / C);
-      s_m2[j] = a2 * (1.f / C);
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        s_m1[warp * RPW + r] = a1[r] * (1.f / C);
+        s_m2[warp * RPW + r] = a2[r] * (1.f / C);
+      }
     }
   }
   __syncthreads();
@@ -728,7 +775,7 @@ static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk
     if (rc) return rc;
   }
   if (stages & 4) {
-    const int tiles = (int)((NN + 63) / 64);
+    const int tiles = (int)((NN + 31) / 32);
     trimul_xnorm_fwd_kernel<C><<<(unsigned)(B * tiles), 256, 0, stream>>>(x_cm, gout, bout, xln, mean_out, rstd_out,
                                                                           NN, tiles);
     TPF_LAUNCH_OK();
