@@ -319,6 +319,35 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared (no registers in between); `valid` false writes zeros.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc),
+               "r"(valid ? 16 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Four 8x8 matrices of 16-bit elements from shared memory, each transposed on the way: lanes 8m..8m+7
+// give the addresses of the eight 16-byte rows of matrix m; lane T receives, in r[m], the elements
+// [2 (T % 4)][T / 4] (low half) and [2 (T % 4) + 1][T / 4] (high half) of the stored matrix m.
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr)
+               : "memory");
+}
+// The inverse direction: lane T holds, in r[m], the elements [T / 4][2 (T % 4)] and [T / 4][2 (T % 4) + 1]
+// of a matrix whose TRANSPOSE is written to the eight 16-byte rows addressed by lanes 8m..8m+7.
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t smem_addr, const uint32_t (&r)[4]) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(smem_addr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -132,87 +132,105 @@ __global__ void __launch_bounds__(256) trimul_ln_fwd_kernel(const bf16* __restri
 // =============================================================================================
 // Output norm forward: channel-major x [B*C][NN] -> row-major LayerNorm(x) [R,C] + mean/rstd
 // =============================================================================================
+// The channel-major -> row-major turn is done on 8x8 blocks of bf16 by ldmatrix.trans instead of element by
+// element through shared memory: the tile is stored as it is loaded (16 bytes = 8 pair rows of one
+// channel), every lane then holds, per 8-channel group, two neighbouring channels of ONE pair row, so
+// the LayerNorm statistics are a register sum plus two shuffles, and the normalised row goes back
+// through a row-major staging tile that is read out in 16-byte pieces.  About one shared-memory
+// instruction per element instead of four.
 template <int C>
-__global__ void __launch_bounds__(256) trimul_xnorm_fwd_kernel(const bf16* __restrict__ x_cm,
-                                                               const float* __restrict__ gamma,
-                                                               const float* __restrict__ beta, bf16* __restrict__ xln,
-                                                               float* __restrict__ mean, float* __restrict__ rstd,
-                                                               int64_t NN, int tiles_per_batch) {
-  // 32 rows per CTA: small tiles keep a dozen CTAs per SM in flight, which is what hides the
-  // load -> transpose -> reduce -> store chain of each of them
-  constexpr int TR = 32;
-  constexpr int RPW = TR / 8;  // rows per warp, handled together so that their reductions overlap
-  __shared__ float tile[C][TR + 1];
-  const int bb = blockIdx.x / tiles_per_batch;
-  const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * TR;
-  // 16-byte loads: 8 consecutive rows of one channel (NN is a multiple of 8)
-#pragma unroll
-  for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
-    const int c = idx / (TR / 8), j8 = idx % (TR / 8);
-    uint4 u = make_uint4(0u, 0u, 0u, 0u);
-    if (r0 + 8 * j8 < NN) u = *reinterpret_cast<const uint4*>(x_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      tile[c][8 * j8 + 2 * e] = bf16_lo(w[e]);
-      tile[c][8 * j8 + 2 * e + 1] = bf16_hi(w[e]);
-    }
-  }
-  __syncthreads();
+__global__ void __launch_bounds__(256, 2) trimul_xnorm_fwd_kernel(const bf16* __restrict__ x_cm,
+                                                                  const float* __restrict__ gamma,
+                                                                  const float* __restrict__ beta,
+                                                                  bf16* __restrict__ xln, float* __restrict__ mean,
+                                                                  float* __restrict__ rstd, int64_t NN,
+                                                                  int tiles_per_batch, int n_tiles) {
+  constexpr int TR = 64;                    // pair rows per tile; warp w owns rows 8w .. 8w+7
+  constexpr int IN_PITCH = TR * 2 + 16;     // bytes per channel row of the input tile (+16: conflict-free ldmatrix)
+  constexpr int OUT_PITCH = C * 2 + 16;     // bytes per pair row of the staging tile
+  constexpr int NG = C / 32;                // ldmatrix.x4 steps: 4 groups of 8 channels each
+  extern __shared__ __align__(16) uint8_t xnorm_smem[];
+  uint8_t* xs0 = xnorm_smem;                       // two input tiles: the next one is fetched (cp.async)
+  uint8_t* ys = xnorm_smem + 2 * C * IN_PITCH;     // while the current one is processed
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int CPL = C / 32;  // channels per lane: lane, lane + 32, ...
-  float v[RPW][CPL], s1[RPW], s2[RPW];
+  const int k2 = 2 * (lane & 3);            // this lane's channel pair inside an 8-channel group
+  const int rr = 8 * warp + (lane >> 2);    // this lane's pair row inside the tile
+  float2 g[NG][4], bt[NG][4];
 #pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    const int j = warp * RPW + r;
-    s1[r] = 0.f;
-    s2[r] = 0.f;
+  for (int i = 0; i < NG; ++i)
 #pragma unroll
-    for (int k = 0; k < CPL; ++k) {
-      v[r][k] = tile[lane + 32 * k][j];
-      s1[r] += v[r][k];
-      s2[r] += v[r][k] * v[r][k];
+    for (int m = 0; m < 4; ++m) {
+      g[i][m] = *reinterpret_cast<const float2*>(gamma + 32 * i + 8 * m + k2);
+      bt[i][m] = *reinterpret_cast<const float2*>(beta + 32 * i + 8 * m + k2);
     }
-  }
+  // 16-byte copies: 8 consecutive pair rows of one channel (NN is a multiple of 8)
+  auto fetch = [&](int tile, uint8_t* dst) {
+    const int fb = tile / tiles_per_batch;
+    const int64_t f0 = (int64_t)(tile % tiles_per_batch) * TR;
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-      s1[r] += __shfl_xor_sync(0xffffffffu, s1[r], off);
-      s2[r] += __shfl_xor_sync(0xffffffffu, s2[r], off);
+    for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
+      const int c = idx / (TR / 8), j8 = idx % (TR / 8);
+      const bool ok = f0 + 8 * j8 < NN;
+      cp_async_16(dst + c * IN_PITCH + 16 * j8, x_cm + ((int64_t)fb * C + c) * NN + (ok ? f0 + 8 * j8 : 0), ok);
     }
-  }
-  float g[CPL], bt[CPL];
-#pragma unroll
-  for (int k = 0; k < CPL; ++k) {
-    g[k] = gamma[lane + 32 * k];
-    bt[k] = beta[lane + 32 * k];
-  }
-  __syncthreads();  // every warp has read its rows: the tile is reused for the normalised values
-#pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    const int j = warp * RPW + r;
-    const float mu = s1[r] * (1.f / C);
-    const float rs = rsqrtf(fmaxf(s2[r] * (1.f / C) - mu * mu, 0.f) + 1e-5f);
-#pragma unroll
-    for (int k = 0; k < CPL; ++k) tile[lane + 32 * k][j] = (v[r][k] - mu) * rs * g[k] + bt[k];
-    if (lane == 0 && r0 + j < NN) {
-      mean[(int64_t)bb * NN + r0 + j] = mu;
-      rstd[(int64_t)bb * NN + r0 + j] = rs;
+    cp_async_commit();
+  };
+  int buf = 0;
+  if ((int)blockIdx.x < n_tiles) fetch(blockIdx.x, xs0);
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, buf ^= 1) {
+    const int bb = tile / tiles_per_batch;
+    const int64_t r0 = (int64_t)(tile % tiles_per_batch) * TR;
+    uint8_t* xs = xs0 + buf * C * IN_PITCH;
+    // the other buffer was last read (ldmatrix) before the barriers of the previous iteration
+    if (tile + (int)gridDim.x < n_tiles) {
+      fetch(tile + gridDim.x, xs0 + (buf ^ 1) * C * IN_PITCH);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-  }
-  __syncthreads();
-  // row-major stores: 16 bytes (8 channels) per thread, a warp covers two whole rows
-  for (int idx = threadIdx.x; idx < TR * (C / 8); idx += 256) {
-    const int j = idx / (C / 8), c8 = idx % (C / 8);
-    if (r0 + j < NN) {
-      uint4 o;
-      o.x = pack_bf16x2(tile[8 * c8 + 0][j], tile[8 * c8 + 1][j]);
-      o.y = pack_bf16x2(tile[8 * c8 + 2][j], tile[8 * c8 + 3][j]);
-      o.z = pack_bf16x2(tile[8 * c8 + 4][j], tile[8 * c8 + 5][j]);
-      o.w = pack_bf16x2(tile[8 * c8 + 6][j], tile[8 * c8 + 7][j]);
-      *reinterpret_cast<uint4*>(xln + ((int64_t)bb * NN + r0 + j) * C + 8 * c8) = o;
+    __syncthreads();
+    uint32_t fr[NG][4];
+#pragma unroll
+    for (int i = 0; i < NG; ++i)
+      ldmatrix_x4_trans(fr[i], smem_u32(xs + (32 * i + lane) * IN_PITCH + 16 * warp));
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NG; ++i)
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const float v0 = bf16_lo(fr[i][m]), v1 = bf16_hi(fr[i][m]);
+        s1 += v0 + v1;
+        s2 += v0 * v0 + v1 * v1;
+      }
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+    const float mu = s1 * (1.f / C);
+    const float rs = rsqrtf(fmaxf(s2 * (1.f / C) - mu * mu, 0.f) + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < NG; ++i)
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const float y0 = (bf16_lo(fr[i][m]) - mu) * rs * g[i][m].x + bt[i][m].x;
+        const float y1 = (bf16_hi(fr[i][m]) - mu) * rs * g[i][m].y + bt[i][m].y;
+        *reinterpret_cast<uint32_t*>(ys + rr * OUT_PITCH + (32 * i + 8 * m + k2) * 2) = pack_bf16x2(y0, y1);
+      }
+    if ((lane & 3) == 0 && r0 + rr < NN) {
+      mean[(int64_t)bb * NN + r0 + rr] = mu;
+      rstd[(int64_t)bb * NN + r0 + rr] = rs;
     }
+    __syncthreads();
+    // row-major stores: 16 bytes (8 channels) per thread, a warp covers two whole rows
+#pragma unroll
+    for (int idx = threadIdx.x; idx < TR * (C / 8); idx += 256) {
+      const int j = idx / (C / 8), c8 = idx % (C / 8);
+      if (r0 + j < NN)
+        *reinterpret_cast<uint4*>(xln + ((int64_t)bb * NN + r0 + j) * C + 8 * c8) =
+            *reinterpret_cast<const uint4*>(ys + j * OUT_PITCH + 16 * c8);
+    }
+    // the next iteration's first barrier orders these reads before the staging tile is rewritten; the
+    // input tile is rewritten only after every warp has passed the barrier above, i.e. after its ldmatrix
   }
 }
 
@@ -426,143 +444,159 @@ __global__ void __launch_bounds__(256) trimul_out_gate_bwd_kernel(const bf16* __
   }
 }
 
-// Output-norm backward.  d_xln row-major [R,C], x channel-major -> d_x channel-major; per-block
-// partial sums for d_gamma / d_beta (fixed order inside the block, folded in block order later).
+// Output-norm backward.  d_xln row-major [R,C], x channel-major -> d_x channel-major; per-CTA partial sums
+// for d_gamma / d_beta (fixed order inside the CTA, folded in CTA order later).
+//
+// Same data movement as the forward norm: x is stored as loaded and turned by ldmatrix.trans, so that a
+// lane holds, for ONE pair row, two neighbouring channels of each 8-channel group; d_xln is staged
+// row-major and read back in that same arrangement; d_x goes back through stmatrix.trans into the
+// channel-major tile (in place: a warp only touches its own 8 pair rows of every channel) and leaves
+// in 16-byte pieces.  The d_gamma / d_beta sums of a lane's channels stay in registers over all the
+// tiles of the CTA and are reduced once at the end.
 template <int C>
-__global__ void __launch_bounds__(256) trimul_xnorm_bwd_kernel(const bf16* __restrict__ d_xln,
-                                                               const bf16* __restrict__ x_cm,
-                                                               const float* __restrict__ gamma,
-                                                               const float* __restrict__ mean,
-                                                               const float* __restrict__ rstd, bf16* __restrict__ dx_cm,
-                                                               float* __restrict__ partials, int64_t NN,
-                                                               int tiles_per_batch) {
-  constexpr int TR = 32;  // rows per CTA (keeps 6 CTAs per SM resident)
-  extern __shared__ float sm[];
-  float(*xh)[TR + 1] = reinterpret_cast<float(*)[TR + 1]>(sm);                  // xhat [C][TR+1]
-  float(*dg)[TR + 1] = reinterpret_cast<float(*)[TR + 1]>(sm + C * (TR + 1));  // d_xln [C][TR+1]
-  __shared__ float s_m1[TR], s_m2[TR], s_rs[TR], s_mu[TR];
-  const int bb = blockIdx.x / tiles_per_batch;
-  const int64_t r0 = (int64_t)(blockIdx.x % tiles_per_batch) * TR;
-  if (threadIdx.x < TR) {
-    const bool ok = r0 + threadIdx.x < NN;
-    s_mu[threadIdx.x] = ok ? mean[(int64_t)bb * NN + r0 + threadIdx.x] : 0.f;
-    s_rs[threadIdx.x] = ok ? rstd[(int64_t)bb * NN + r0 + threadIdx.x] : 0.f;
-  }
-  __syncthreads();
-  // x (channel-major): 8 consecutive rows of one channel per 16-byte load
-  for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
-    const int c = idx / (TR / 8), j8 = idx % (TR / 8);
-    uint4 u = make_uint4(0u, 0u, 0u, 0u);
-    const bool ok = r0 + 8 * j8 < NN;
-    if (ok) u = *reinterpret_cast<const uint4*>(x_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int j = 8 * j8 + 2 * e;
-      xh[c][j] = ok ? (bf16_lo(w[e]) - s_mu[j]) * s_rs[j] : 0.f;
-      xh[c][j + 1] = ok ? (bf16_hi(w[e]) - s_mu[j + 1]) * s_rs[j + 1] : 0.f;
-    }
-  }
-  // d_xln (row-major): 8 consecutive channels of one row per 16-byte load.  A warp takes 8 rows x 4
-  // channel groups, which makes the transposed stores below bank-conflict free (bank = 8*(lane&3) +
-  // (lane>>2) + const with the 33-word pitch).
-  for (int idx = threadIdx.x; idx < TR * (C / 8); idx += 256) {
-    const int ln = idx & 31, grp = idx >> 5;
-    const int c8 = (ln & 3) + 4 * (grp % (C / 32)), j = (ln >> 2) + 8 * (grp / (C / 32));
-    uint4 u = make_uint4(0u, 0u, 0u, 0u);
-    if (r0 + j < NN) u = *reinterpret_cast<const uint4*>(d_xln + ((int64_t)bb * NN + r0 + j) * C + 8 * c8);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      dg[8 * c8 + 2 * e][j] = bf16_lo(w[e]);
-      dg[8 * c8 + 2 * e + 1][j] = bf16_hi(w[e]);
-    }
-  }
-  __syncthreads();
+__global__ void __launch_bounds__(256, 2) trimul_xnorm_bwd_kernel(const bf16* __restrict__ d_xln,
+                                                                  const bf16* __restrict__ x_cm,
+                                                                  const float* __restrict__ gamma,
+                                                                  const float* __restrict__ mean,
+                                                                  const float* __restrict__ rstd,
+                                                                  bf16* __restrict__ dx_cm, float* __restrict__ partials,
+                                                                  int64_t NN, int tiles_per_batch, int n_tiles) {
+  constexpr int TR = 64;
+  constexpr int IN_PITCH = TR * 2 + 16;
+  constexpr int OUT_PITCH = C * 2 + 16;
+  constexpr int NG = C / 32;
+  extern __shared__ __align__(16) uint8_t xnorm_smem[];
+  // two (x, d_xln) tile pairs: the next pair is fetched (cp.async) while the current one is processed
+  uint8_t* xs0 = xnorm_smem;                          // x, later d_x: [channel][pair row]
+  uint8_t* ds0 = xnorm_smem + 2 * C * IN_PITCH;       // d_xln: [pair row][channel]
+  __shared__ float2 gsm[C / 2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  {
-    // the four rows of a warp are reduced together so that their shuffle chains overlap
-    constexpr int RPW = TR / 8;
-    float a1[RPW], a2[RPW];
+  const int k2 = 2 * (lane & 3);
+  const int rr = 8 * warp + (lane >> 2);
+  if (threadIdx.x < C / 2) gsm[threadIdx.x] = *reinterpret_cast<const float2*>(gamma + 2 * threadIdx.x);
+  float2 ag[NG][4], ab[NG][4];  // running sums of d * xhat and d for this lane's channels
 #pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-      a1[r] = 0.f;
-      a2[r] = 0.f;
+  for (int i = 0; i < NG; ++i)
+#pragma unroll
+    for (int m = 0; m < 4; ++m) ag[i][m] = ab[i][m] = make_float2(0.f, 0.f);
+
+  auto fetch = [&](int tile, uint8_t* xdst, uint8_t* ddst) {
+    const int fb = tile / tiles_per_batch;
+    const int64_t f0 = (int64_t)(tile % tiles_per_batch) * TR;
+#pragma unroll
+    for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
+      const int c = idx / (TR / 8), j8 = idx % (TR / 8);
+      const bool ok = f0 + 8 * j8 < NN;
+      cp_async_16(xdst + c * IN_PITCH + 16 * j8, x_cm + ((int64_t)fb * C + c) * NN + (ok ? f0 + 8 * j8 : 0), ok);
     }
 #pragma unroll
-    for (int c = lane; c < C; c += 32) {
-      const float gm = gamma[c];
-#pragma unroll
-      for (int r = 0; r < RPW; ++r) {
-        const int j = warp * RPW + r;
-        const float g = gm * dg[c][j];
-        a1[r] += g;
-        a2[r] += g * xh[c][j];
-      }
+    for (int idx = threadIdx.x; idx < TR * (C / 8); idx += 256) {
+      const int j = idx / (C / 8), c8 = idx % (C / 8);
+      const bool ok = f0 + j < NN;
+      cp_async_16(ddst + j * OUT_PITCH + 16 * c8, d_xln + ((int64_t)fb * NN + (ok ? f0 + j : 0)) * C + 8 * c8, ok);
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-      for (int r = 0; r < RPW; ++r) {
-        a1[r] += __shfl_xor_sync(0xffffffffu, a1[r], off);
-        a2[r] += __shfl_xor_sync(0xffffffffu, a2[r], off);
-      }
+    cp_async_commit();
+  };
+  int buf = 0;
+  if ((int)blockIdx.x < n_tiles) fetch(blockIdx.x, xs0, ds0);
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, buf ^= 1) {
+    const int bb = tile / tiles_per_batch;
+    const int64_t r0 = (int64_t)(tile % tiles_per_batch) * TR;
+    uint8_t* xs = xs0 + buf * C * IN_PITCH;
+    uint8_t* ds = ds0 + buf * TR * OUT_PITCH;
+    const bool row_ok = r0 + rr < NN;
+    const float mu = row_ok ? mean[(int64_t)bb * NN + r0 + rr] : 0.f;
+    const float rs = row_ok ? rstd[(int64_t)bb * NN + r0 + rr] : 0.f;
+    // The other buffer pair was last touched in the previous iteration: its d_x read-out (plain loads) was
+    // completed by every thread before that thread got here, but by OTHER threads only if they are past it too
+    __syncthreads();
+    if (tile + (int)gridDim.x < n_tiles) {
+      fetch(tile + gridDim.x, xs0 + (buf ^ 1) * C * IN_PITCH, ds0 + (buf ^ 1) * TR * OUT_PITCH);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    if (lane == 0) {
+    __syncthreads();
+    uint32_t fx[NG][4], fd[NG][4];
 #pragma unroll
-      for (int r = 0; r < RPW; ++r) {
-        s_m1[warp * RPW + r] = a1[r] * (1.f / C);
-        s_m2[warp * RPW + r] = a2[r] * (1.f / C);
+    for (int i = 0; i < NG; ++i) {
+      ldmatrix_x4_trans(fx[i], smem_u32(xs + (32 * i + lane) * IN_PITCH + 16 * warp));
+#pragma unroll
+      for (int m = 0; m < 4; ++m)
+        fd[i][m] = *reinterpret_cast<const uint32_t*>(ds + rr * OUT_PITCH + (32 * i + 8 * m + k2) * 2);
+    }
+    float a1 = 0.f, a2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NG; ++i)
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const float2 gm = gsm[(32 * i + 8 * m + k2) >> 1];
+        const float x0 = (bf16_lo(fx[i][m]) - mu) * rs, x1 = (bf16_hi(fx[i][m]) - mu) * rs;
+        const float d0 = bf16_lo(fd[i][m]), d1 = bf16_hi(fd[i][m]);
+        const float g0 = gm.x * d0, g1 = gm.y * d1;
+        a1 += g0 + g1;
+        a2 += g0 * x0 + g1 * x1;
+        ag[i][m].x += d0 * x0;
+        ag[i][m].y += d1 * x1;
+        ab[i][m].x += d0;
+        ab[i][m].y += d1;
       }
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+    a2 += __shfl_xor_sync(0xffffffffu, a2, 1);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+    a2 += __shfl_xor_sync(0xffffffffu, a2, 2);
+    const float m1 = a1 * (1.f / C), m2 = a2 * (1.f / C);
+#pragma unroll
+    for (int i = 0; i < NG; ++i) {
+      uint32_t out[4];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const float2 gm = gsm[(32 * i + 8 * m + k2) >> 1];
+        const float x0 = (bf16_lo(fx[i][m]) - mu) * rs, x1 = (bf16_hi(fx[i][m]) - mu) * rs;
+        const float v0 = rs * (gm.x * bf16_lo(fd[i][m]) - m1 - x0 * m2);
+        const float v1 = rs * (gm.y * bf16_hi(fd[i][m]) - m1 - x1 * m2);
+        out[m] = pack_bf16x2(v0, v1);
+      }
+      stmatrix_x4_trans(smem_u32(xs + (32 * i + lane) * IN_PITCH + 16 * warp), out);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int idx = threadIdx.x; idx < C * (TR / 8); idx += 256) {
+      const int c = idx / (TR / 8), j8 = idx % (TR / 8);
+      if (r0 + 8 * j8 < NN)
+        *reinterpret_cast<uint4*>(dx_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8) =
+            *reinterpret_cast<const uint4*>(xs + c * IN_PITCH + 16 * j8);
     }
   }
+
+  // ---- d_gamma / d_beta partials of this CTA: the 8 pair rows of a warp (lanes that differ in lane / 4) in
+  //      shuffle order, then the 8 warps in warp order; a fixed tree, no atomics
   __syncthreads();
-  // Four adjacent lanes share a channel (8 rows each).  The same pass forms d_x and the block's
-  // d_gamma / d_beta partials: 8-row sums in ascending row order, then the four lanes' sums in lane
-  // order (fixed order, no atomics).  Every lane of a warp takes part in the shuffles.
-  {
-    const int j8 = threadIdx.x % (TR / 8);  // the same for every idx of this thread (256 % (TR/8) == 0)
-    float rs8[8], m18[8], m28[8];
+  float* red = reinterpret_cast<float*>(ds0);  // [8 warps][2][C]
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      rs8[e] = s_rs[8 * j8 + e];
-      m18[e] = s_m1[8 * j8 + e];
-      m28[e] = s_m2[8 * j8 + e];
-    }
-    const bool rows_ok = r0 + 8 * j8 < NN;
-    for (int base = 0; base < C * (TR / 8); base += 256) {
-      const int idx = base + threadIdx.x;
-      const bool live = idx < C * (TR / 8);  // uniform per warp (C * TR / 8 is a multiple of 32)
-      const int c = live ? idx / (TR / 8) : 0;
-      const float gc = gamma[c];
-      float v[8], sg = 0.f, sb = 0.f;
+  for (int i = 0; i < NG; ++i)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int j = 8 * j8 + e;
-        const float d = dg[c][j], x = xh[c][j];
-        v[e] = rs8[e] * (gc * d - m18[e] - x * m28[e]);
-        sg += d * x;
-        sb += d;
-      }
-      if (!live) continue;
-      if (rows_ok) {
-        uint4 o;
-        o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-        o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-        *reinterpret_cast<uint4*>(dx_cm + ((int64_t)bb * C + c) * NN + r0 + 8 * j8) = o;
-      }
-      const int l0 = (threadIdx.x & 31) & ~3;
-      float tg = __shfl_sync(0xffffffffu, sg, l0), tb = __shfl_sync(0xffffffffu, sb, l0);
+    for (int m = 0; m < 4; ++m) {
+      float v[4] = {ag[i][m].x, ag[i][m].y, ab[i][m].x, ab[i][m].y};
 #pragma unroll
-      for (int k = 1; k < 4; ++k) {
-        tg += __shfl_sync(0xffffffffu, sg, l0 + k);
-        tb += __shfl_sync(0xffffffffu, sb, l0 + k);
-      }
-      if (j8 == 0) {
-        partials[(int64_t)blockIdx.x * 2 * C + c] = tg;
-        partials[(int64_t)blockIdx.x * 2 * C + C + c] = tb;
+      for (int off = 4; off < 32; off <<= 1)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] += __shfl_xor_sync(0xffffffffu, v[e], off);
+      if (lane < 4) {
+        const int c = 32 * i + 8 * m + k2;
+        red[(warp * 2 + 0) * C + c] = v[0];
+        red[(warp * 2 + 0) * C + c + 1] = v[1];
+        red[(warp * 2 + 1) * C + c] = v[2];
+        red[(warp * 2 + 1) * C + c + 1] = v[3];
       }
     }
+  __syncthreads();
+  if (threadIdx.x < 2 * C) {
+    const int which = threadIdx.x / C, c = threadIdx.x % C;
+    float t = red[(0 * 2 + which) * C + c];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t += red[(w * 2 + which) * C + c];
+    partials[(int64_t)blockIdx.x * 2 * C + which * C + c] = t;
   }
 }
 
@@ -775,9 +809,16 @@ static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk
     if (rc) return rc;
   }
   if (stages & 4) {
-    const int tiles = (int)((NN + 31) / 32);
-    trimul_xnorm_fwd_kernel<C><<<(unsigned)(B * tiles), 256, 0, stream>>>(x_cm, gout, bout, xln, mean_out, rstd_out,
-                                                                          NN, tiles);
+    const int tiles = (int)((NN + 63) / 64);
+    int grid = (int)(B * tiles);
+    if (grid > 2 * sm_count()) grid = 2 * sm_count();
+    {
+      auto kern = trimul_xnorm_fwd_kernel<C>;
+      constexpr int smem = 2 * C * (64 * 2 + 16) + 64 * (C * 2 + 16);
+      static PerDeviceOnce once;  // per instantiation
+      if ((rc = ensure_dynamic_smem(kern, smem, once))) return rc;
+      kern<<<grid, 256, smem, stream>>>(x_cm, gout, bout, xln, mean_out, rstd_out, NN, tiles, (int)(B * tiles));
+    }
     TPF_LAUNCH_OK();
     using Cfg = GemmCfg<128, C, 128, false, 128, false, 4>;
     GemmShape sh{(int)R, C, C, 1, 0};
@@ -825,7 +866,11 @@ static void plan_bwd_workspace(int64_t B, int64_t NN, int64_t C, char* base, Tri
   split_plan(R, 1, &w->splits_wz, &w->kps_wz);
   w->part_w5 = reinterpret_cast<float*>(take((int64_t)w->splits_w5 * 5 * C * C * 4));
   w->part_wz = reinterpret_cast<float*>(take((int64_t)w->splits_wz * C * C * 4));
-  w->blocks_ln_out = (int)(B * ((NN + 31) / 32));
+  {
+    // one partial row per CTA of the output-norm backward kernel (persistent, two CTAs per SM)
+    const int64_t tiles = B * ((NN + 63) / 64);
+    w->blocks_ln_out = (int)(tiles < 2 * sm_count() ? tiles : 2 * sm_count());
+  }
   w->rows_per_block_in = 256;
   w->blocks_ln_in = (int)((R + 255) / 256);
   w->part_ln_out = reinterpret_cast<float*>(take((int64_t)w->blocks_ln_out * 2 * C * 4));
@@ -883,13 +928,15 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
   }
   // 3. output norm backward -> d_x (channel-major), d_gamma_out, d_beta_out
   {
-    const int tiles = (int)((NN + 31) / 32);
-    auto kern = trimul_xnorm_bwd_kernel<C>;
-    const int smem = 2 * C * 33 * 4;
-    static PerDeviceOnce once;  // per instantiation
-    if ((rc = ensure_dynamic_smem(kern, smem, once))) return rc;
-    kern<<<(unsigned)(B * tiles), 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out,
-                                                       NN, tiles);
+    const int tiles = (int)((NN + 63) / 64);
+    {
+      auto kern = trimul_xnorm_bwd_kernel<C>;
+      constexpr int smem = 2 * C * (64 * 2 + 16) + 2 * 64 * (C * 2 + 16);
+      static PerDeviceOnce once;  // per instantiation
+      if ((rc = ensure_dynamic_smem(kern, smem, once))) return rc;
+      kern<<<w.blocks_ln_out, 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out, NN,
+                                                  tiles, (int)(B * tiles));
+    }
     TPF_LAUNCH_OK();
     {
       const int lvl = (w.blocks_ln_out + 255) / 256;
