@@ -111,7 +111,11 @@ struct AttnBwdCfg {
   static constexpr int OFF_K = OFF_DO + NQ * TILE;       // [NKV]
   static constexpr int OFF_V = OFF_K + NKV * TILE;       // [NKV]
   static constexpr int OFF_MASK = OFF_V + NKV * TILE;    // [NKV] x 512
-  static constexpr int OFF_BAR = OFF_MASK + NKV * 512;
+  // two staging tiles through which finished dQ / dK / dV tiles leave as whole, contiguous 128 x D blocks
+  // (only where shared memory has room for them; otherwise every thread stores its own piece)
+  static constexpr int OFF_STG = OFF_MASK + NKV * 512;
+  static constexpr bool STAGED = OFF_STG + 2 * TILE + 1024 + 256 <= 232448 - 1024;
+  static constexpr int OFF_BAR = OFF_STG + (STAGED ? 2 * TILE : 0);
   static constexpr int N_BAR = 2 * NB + 2 * NQ + 2 * NKV + 6;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
   static constexpr int TM_S = 0, TM_DP = 128, TM_DQ = 256, TM_DK = 320, TM_DV = 320 + KS * D;
@@ -368,7 +372,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           umma_commit(&q_empty[bq_s]);
           if (++bq_s == NQ) bq_s = 0;
         }
-        if (strip_done) umma_commit(dkv_full);
+        (void)strip_done;  // the compute warps learn of a finished strip from pds_free of its last tile
         wb.next();
       }
     }
@@ -392,8 +396,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t sdpfull_ph = 0, pdsfree_ph = 1, kv_ph = 0, b_ph = 0, dkvfull_ph = 0;
     int kv_s = 0, b_s = 0;
     float neg_lse2 = -INFINITY, delta = 0.f;
-    bool have_prev_dq = false;  // a finished dQ tile waits in TMEM
+    bool have_prev_dq = false;     // a finished dQ tile waits in TMEM
+    bool have_prev_strip = false;  // the dK / dV accumulators of a finished strip wait in TMEM
     int prev_q0 = 0, prev_b = 0, prev_o = 0, prev_h = 0, prev_strip = 0;
+    int sp_b = 0, sp_o = 0, sp_h = 0, sp_strip = 0, sp_nk = 0;
+    int stg_slot = 0;
 
     // read DQ consecutive accumulator columns of this thread's row
     auto ld_cols = [&](uint32_t taddr, float (&v)[DQ]) {
@@ -426,8 +433,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     };
 
+    // One finished 128 x D tile (this thread holds DQ columns of row `row`) -> global memory at `gtile`
+    // (row 0 of the tile; the tile is one contiguous block there).  Staged: every thread drops its piece
+    // into a shared-memory copy of the block, then the 512 compute threads write the block out in
+    // consecutive 16-byte pieces, so each store instruction covers 512 contiguous bytes instead of 32
+    // half-used sectors.  All sixteen compute warps call this together.
+    auto store_tile = [&](__nv_bfloat16* gtile, int rows_valid, const float (&v)[DQ], float mul) {
+      if constexpr (Cfg::STAGED) {
+        uint8_t* stg = smem + Cfg::OFF_STG + stg_slot * Cfg::TILE;
+        stg_slot ^= 1;
+        st_cols(reinterpret_cast<__nv_bfloat16*>(stg) + row * D + DQ * part, v, mul);
+        named_barrier_sync(1, 32 * NCW);
+#pragma unroll
+        for (int i = threadIdx.x; i < Cfg::TILE / 16; i += 32 * NCW)
+          if ((16 * i) / (2 * D) < rows_valid)
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(gtile) + 16 * i) = *reinterpret_cast<const uint4*>(stg + 16 * i);
+      } else {
+        if (row < rows_valid) st_cols(gtile + row * D + DQ * part, v, mul);
+      }
+    };
+
     // store a finished dQ tile that has been read out of TMEM (or fold it into the per-CTA running sum)
     auto store_dq = [&](int b, int o, int h, int q0, int strip, float (&v)[DQ]) {
+      if (p.n_strips == 1) {
+        store_tile(p.dq + ((((int64_t)b * p.O + o) * p.H + h) * p.N + q0) * D, p.N - q0, v, scale);
+        return;
+      }
       const int q = q0 + row;
       if (q >= p.N) return;
       if (p.n_strips > 1) {
@@ -462,6 +493,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           l_pref = __ldg(p.lse + idx);
           d_pref = __ldg(p.delta + idx);
         }
+      }
+    };
+
+    // Reads finished accumulators out of TMEM and sends them on their way: the dQ tile of a finished query
+    // tile and, after the last tile of a strip, the strip's dK / dV tiles (then the UMMA issuer may start the
+    // next strip in those columns).  Called by all compute warps once the UMMAs of the previous tile are done.
+    auto drain_finished = [&]() {
+      if (have_prev_dq) {
+        float dqv[DQ];
+        ld_cols(t_dq, dqv);
+        have_prev_dq = false;
+        store_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip, dqv);
+      }
+      if (have_prev_strip) {
+        have_prev_strip = false;
+        for (int kk = 0; kk < sp_nk; ++kk) {
+          const int key0 = (sp_strip * KS + kk) * 128;
+          const int64_t base = ((((int64_t)sp_b * p.O + sp_o) * p.H + sp_h) * p.N + key0) * D;
+          float vk1[DQ], vv1[DQ];
+          ld_cols(tmem_addr(tmem_base, lane_base, Cfg::TM_DK + kk * D + DQ * part), vk1);
+          ld_cols(tmem_addr(tmem_base, lane_base, Cfg::TM_DV + kk * D + DQ * part), vv1);
+          store_tile(p.dk + base, p.N - key0, vk1, scale);
+          store_tile(p.dv + base, p.N - key0, vv1, 1.f);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dkv_free);
+      } else {
+        tc_fence_before();
       }
     };
 
@@ -559,13 +619,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_wait(pds_free, pdsfree_ph, wctx);
       pdsfree_ph ^= 1;
       tc_fence_after();
-      float dqv[DQ];
-      const bool store_prev = have_prev_dq;
-      if (store_prev) {
-        ld_cols(t_dq, dqv);
-        have_prev_dq = false;
-        tc_fence_before();
-      }
+      // the same completion covers the last tile of a strip: its dQ and the strip's dK / dV leave now,
+      // before this tile's P / dS release the UMMAs that would overwrite them
+      drain_finished();
       {
         uint8_t* p_row = smem + Cfg::OFF_P + half_off;
         uint8_t* ds_row = smem + Cfg::OFF_DS + half_off;
@@ -579,41 +635,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_ready);
-      if (store_prev) store_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip, dqv);
 
       if (w.last_kk()) {
         have_prev_dq = true;
         prev_b = b; prev_o = o; prev_h = h; prev_q0 = w.qt * 128; prev_strip = w.strip;
       }
-
       if (w.last_kk() && w.last_qt()) {
-        // ---------------- strip epilogue: dQ of the last query tile, dK / dV of the strip
-        mbar_wait(dkv_full, dkvfull_ph, wctx);
-        dkvfull_ph ^= 1;
-        tc_fence_after();
-        ld_cols(t_dq, dqv);
-        have_prev_dq = false;
-        store_dq(prev_b, prev_o, prev_h, prev_q0, prev_strip, dqv);
-        {
-          const int nk = w.strip_len();
-          for (int kk = 0; kk < nk; ++kk) {
-            const int key = (w.strip * KS + kk) * 128 + row;
-            const int64_t base = ((((int64_t)b * p.O + o) * p.H + h) * p.N + key) * D + DQ * part;
-            float vk1[DQ], vv1[DQ];
-            ld_cols(tmem_addr(tmem_base, lane_base, Cfg::TM_DK + kk * D + DQ * part), vk1);
-            ld_cols(tmem_addr(tmem_base, lane_base, Cfg::TM_DV + kk * D + DQ * part), vv1);
-            if (key < p.N) {
-              st_cols(p.dk + base, vk1, scale);
-              st_cols(p.dv + base, vv1, 1.f);
-            }
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(dkv_free);
-        }
+        have_prev_strip = true;
+        sp_b = b; sp_o = o; sp_h = h; sp_strip = w.strip; sp_nk = w.strip_len();
       }
     }
+    // the last tile of this CTA: wait for its UMMAs, then the same drain
+    if (have_prev_dq || have_prev_strip) {
+      mbar_wait(pds_free, pdsfree_ph, wctx);
+      pdsfree_ph ^= 1;
+      tc_fence_after();
+      drain_finished();
+    }
   }
+
 
   tc_fence_before();
   __syncthreads();
@@ -854,13 +894,14 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_after();
       const float* mask_row =
           reinterpret_cast<const float*>(smem + Cfg::OFF_ST + s * Cfg::STAGE + 4 * Cfg::TILE) + CPT * part;
-      const bool general = tail || __any_sync(0xffffffffu, mask_row[lane] != 0.f);
       const uint32_t t_s = tmem_addr(tmem_base, lane_base, buf * 256 + CPT * part);
       const uint32_t t_dp = tmem_addr(tmem_base, lane_base, buf * 256 + 128 + CPT * part);
       // 8 columns per step; the TMEM loads of step c+1 are in flight while step c is computed
       uint32_t rs[2][8], rd[2][8];
       tmem_ld8(t_s, rs[0]);
       tmem_ld8(t_dp, rd[0]);
+      // the mask probe (shared-memory load + vote) runs under the latency of the first TMEM loads
+      const bool general = tail || __any_sync(0xffffffffu, mask_row[lane] != 0.f);
 #pragma unroll
       for (int c = 0; c < CPT / 8; ++c) {
         const float4 bb0 = bias32[((part * 2 + (c >> 1)) * 4 + 2 * (c & 1)) * 128 + row];
