@@ -49,6 +49,7 @@ template <int D>
 __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ d_out,
                                                          const __nv_bfloat16* __restrict__ out,
                                                          float* __restrict__ delta, int64_t rows, int H, int N) {
+  griddep_wait();
   // one thread handles D/8 ... : LANES threads per (b,o,q,h) row of D elements, 8 elements each
   constexpr int LANES = D / 8;
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -161,6 +162,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
                 const AttnBwdParams p, int* __restrict__ status) {
+  griddep_wait();
   constexpr int D = Cfg::D, KS = Cfg::KS, NKV = Cfg::NKV, NQ = Cfg::NQ, NB = Cfg::NB, NCW = Cfg::NCW;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
@@ -711,6 +713,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                   const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
                   const AttnDbiasParams p, int* __restrict__ status) {
+  griddep_wait();
   constexpr int D = Cfg::D, NST = Cfg::NST, NCW = Cfg::NCW;
   constexpr int WARP_TMA = NCW, WARP_MMA = NCW + 1;
   constexpr int CPT = 32;                   // key columns per thread
@@ -984,6 +987,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 // dbias[i] = ((part[0][i] + part[1][i]) + part[2][i]) + ...   (ascending chunk order, fp32)
 __global__ void __launch_bounds__(256) attn_dbias_fold_kernel(const float* __restrict__ part, float* __restrict__ out,
                                                               int64_t n, int n_chunks) {
+  griddep_wait();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     float a = part[i];
     for (int c = 1; c < n_chunks; ++c) a = __fadd_rn(a, part[(int64_t)c * n + i]);
@@ -1007,7 +1011,7 @@ int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
   auto kern = attn_bwd_kernel<Cfg>;
   static PerDeviceOnce once;  // per instantiation
   if (int rc = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, once)) return rc;
-  kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
+  launch_kernel(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, tdo, tb, tmk, p, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }
@@ -1060,9 +1064,9 @@ int attn_bwd_dqkv(const void* q, const void* k, const void* v, const void* d_out
     TPF_REQUIRE(blocks < (1ll << 31), TPF_ERR_INVALID_ARGUMENT, "attn_bwd: too many rows");
     const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(d_out);
     const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(out);
-    if (D == 16) attn_delta_kernel<16><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
-    else if (D == 32) attn_delta_kernel<32><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
-    else attn_delta_kernel<64><<<(unsigned)blocks, 256, 0, stream>>>(a, b, delta, rows, (int)H, (int)N);
+    if (D == 16) launch_kernel(attn_delta_kernel<16>, dim3((unsigned)blocks), dim3(256), 0, stream, a, b, delta, rows, (int)H, (int)N);
+    else if (D == 32) launch_kernel(attn_delta_kernel<32>, dim3((unsigned)blocks), dim3(256), 0, stream, a, b, delta, rows, (int)H, (int)N);
+    else launch_kernel(attn_delta_kernel<64>, dim3((unsigned)blocks), dim3(256), 0, stream, a, b, delta, rows, (int)H, (int)N);
     TPF_LAUNCH_OK();
   }
 
@@ -1110,7 +1114,7 @@ int launch_attn_dbias(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   auto kern = attn_dbias_kernel<Cfg>;
   static PerDeviceOnce once;  // per instantiation
   if (int rc = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, once)) return rc;
-  kern<<<grid, 32 * (Cfg::NCW + 2), Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tb, tmk, p, status);
+  launch_kernel(kern, dim3(grid), dim3(32 * (Cfg::NCW + 2)), Cfg::SMEM_BYTES, stream, tq, tk, tv, tdo, tb, tmk, p, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }
@@ -1184,7 +1188,7 @@ int attn_bwd_dbias(const void* q, const void* k, const void* v, const void* d_ou
     const int64_t n = G * H * N * N;
     int blocks = (int)((n + 255) / 256);
     if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
-    attn_dbias_fold_kernel<<<blocks, 256, 0, stream>>>(p.part, dbias, n, n_chunks);
+    launch_kernel(attn_dbias_fold_kernel, dim3(blocks), dim3(256), 0, stream, p.part, dbias, n, n_chunks);
     TPF_LAUNCH_OK();
   }
   return TPF_OK;

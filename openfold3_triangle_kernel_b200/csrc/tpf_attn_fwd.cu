@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::CTAS_PER_SM)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
                 const __grid_constant__ CUtensorMap tmMask, const AttnFwdParams p, int* __restrict__ status) {
+  griddep_wait();
   constexpr int D = Cfg::D, NKV = Cfg::NKV, NB = Cfg::NB, NMASK = Cfg::NMASK, KEYS = Cfg::KEYS;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
@@ -511,7 +512,7 @@ int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
   if (int rc = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, once)) return rc;
   int grid = Cfg::CTAS_PER_SM * sm_count();
   if (grid > p.n_items) grid = p.n_items;
-  kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tb, tmk, p, status);
+  launch_kernel(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, tb, tmk, p, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }

@@ -91,6 +91,7 @@ struct EpiStore {
     int64_t batch_stride;
   };
   static constexpr bool kPaired = false;
+  static constexpr bool kStaged = false;
   static constexpr int kSmemPerWarp = sizeof(OutT) == 2 ? 2048 : 0;  // bytes of per-warp epilogue scratch
   // Global-memory operands of the epilogue, requested before the accumulator wait so that their
   // latency hides behind the UMMAs instead of stalling the (few) epilogue warps chunk by chunk.
@@ -130,6 +131,7 @@ template <class Cfg, class Epi>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmShape sh, const typename Epi::Params ep, int* __restrict__ status) {
+  griddep_wait();
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   uint8_t* sA = smem;
@@ -256,12 +258,34 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // epilogue warps: EPI_PER_Q per TMEM lane quarter; they interleave 32-column chunks
+    // epilogue warps: EPI_PER_Q per TMEM lane quarter; they interleave 32-column chunks.
+    // The epilogue's global-memory operands of tile t + 1 are requested while tile t is still being
+    // worked on (the accumulators are usually ready long before the epilogue gets to them, so a request
+    // made only at the top of a tile would expose the whole DRAM latency once per tile).
     const int lane_base = 32 * (warp & 3);
     const int chunk_par = (warp - 2) >> 2;
     float* wsm = reinterpret_cast<float*>(epi_smem + (warp - 2) * Epi::kSmemPerWarp);
     int acc = 0;
     uint32_t acc_ph = 0;
+    constexpr int NCH = Epi::kPaired ? (Cfg::BN / 64 + Cfg::EPI_PER_Q - 1) / Cfg::EPI_PER_Q
+                                     : (Cfg::BN / 32 + Cfg::EPI_PER_Q - 1) / Cfg::EPI_PER_Q;
+    auto request = [&](int t, typename Epi::Pre (&pre)[NCH]) {
+      const int b = t / (mt * nt);
+      const int r = t - b * (mt * nt);
+      const int m = (r / nt) * Cfg::BM + lane_base + lane;
+      const int n0 = (r % nt) * Cfg::BN;
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
+        if constexpr (!Epi::kPaired) {
+          if (c < Cfg::BN && n0 + c < sh.N) Epi::prefetch(ep, sh, b, m, n0 + c, lane, pre[k]);
+        } else {
+          if (c < Cfg::BN / 2) Epi::prefetch2(ep, sh, b, m, n0, c, lane, pre[k]);
+        }
+      }
+    };
+    typename Epi::Pre pre[NCH];
+    if ((int)blockIdx.x < tiles) request(blockIdx.x, pre);
     for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
       const int b = t / (mt * nt);
       const int r = t - b * (mt * nt);
@@ -269,23 +293,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = (r % nt) * Cfg::BN;
       const uint32_t t_acc = tmem_addr(tmem_base, lane_base, acc * Cfg::ACC_STRIDE);
       const int m = m0 + lane_base + lane;
+      typename Epi::Pre nxt[NCH];
+      mbar_wait(&tfull[acc], acc_ph, wctx);
+      tc_fence_after();
       if constexpr (!Epi::kPaired) {
-        // all of this warp's 32-column chunks are requested before the single wait
-        constexpr int NCH = (Cfg::BN / 32 + Cfg::EPI_PER_Q - 1) / Cfg::EPI_PER_Q;
-        typename Epi::Pre pre[NCH];
-#pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-          const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
-          if (c < Cfg::BN && n0 + c < sh.N) Epi::prefetch(ep, sh, b, m, n0 + c, lane, pre[k]);
-        }
-        mbar_wait(&tfull[acc], acc_ph, wctx);
-        tc_fence_after();
         uint32_t raw[NCH][32];
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
           const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
           if (c < Cfg::BN) tmem_ld32(t_acc + c, raw[k]);
         }
+        if (t + (int)gridDim.x < tiles) request(t + gridDim.x, nxt);
         tmem_ld_wait();
         // the accumulator now lives in registers: hand the TMEM buffer back before the epilogue math
         tc_fence_before();
@@ -303,15 +321,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       } else {
         // Column c (first half of the tile) pairs with column c + BN/2.
-        constexpr int NCH = (Cfg::BN / 64 + Cfg::EPI_PER_Q - 1) / Cfg::EPI_PER_Q;
-        typename Epi::Pre pre[NCH];
-#pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-          const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
-          if (c < Cfg::BN / 2) Epi::prefetch2(ep, sh, b, m, n0, c, lane, pre[k]);
-        }
-        mbar_wait(&tfull[acc], acc_ph, wctx);
-        tc_fence_after();
         uint32_t raw0[NCH][32], raw1[NCH][32];
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
@@ -321,6 +330,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tmem_ld32(t_acc + Cfg::BN / 2 + c, raw1[k]);
           }
         }
+        // an epilogue that parks its operands in shared memory does so before the next tile's are requested,
+        // so that both sets never hold registers at the same time
+        if constexpr (Epi::kStaged && NCH == 1) Epi::stage(pre[0], wsm, lane);
+        if (t + (int)gridDim.x < tiles) request(t + gridDim.x, nxt);
         tmem_ld_wait();
         // the accumulator now lives in registers: hand the TMEM buffer back before the epilogue math
         tc_fence_before();
@@ -330,6 +343,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int k = 0; k < NCH; ++k) {
           const int c = 32 * (chunk_par + Cfg::EPI_PER_Q * k);
           if (c < Cfg::BN / 2) {
+            if constexpr (Epi::kStaged && NCH > 1) Epi::stage(pre[k], wsm, lane);
             float v0[32], v1[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -340,6 +354,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) pre[k] = nxt[k];
       if (++acc == 2) {
         acc = 0;
         acc_ph ^= 1;

@@ -43,7 +43,7 @@ int launch_gemm(const void* A, int64_t lda, int64_t bsa, const void* B, int64_t 
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid > tiles) grid = tiles;
   if (grid < 1) return TPF_OK;
-  kern<<<grid, Cfg::THREADS, smem_bytes, stream>>>(tmA, tmB, sh, ep, status);
+  launch_kernel(kern, dim3(grid), dim3(Cfg::THREADS), smem_bytes, stream, tmA, tmB, sh, ep, status);
   TPF_LAUNCH_OK();
   return TPF_OK;
 }

@@ -46,7 +46,27 @@ inline std::atomic<long long>& launch_counter() {
   return n;
 }
 
-// After every <<<...>>>: count the launch and surface a launch error.
+// Every kernel of the library is launched with programmatic stream serialization: the launch is set up
+// while the preceding kernel of the stream still runs, and the kernel itself holds at `griddep_wait()`
+// (its first statement that can touch global memory) until that kernel has completed and its writes are
+// visible.  Results are those of plain stream order; the launch latency between dependent kernels is hidden.
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);  // the error is read by TPF_LAUNCH_OK()
+}
+
+// After every launch_kernel(...): count the launch and surface a launch error.
 #define TPF_LAUNCH_OK()                          \
   do {                                           \
     ::tpf::launch_counter().fetch_add(1);        \

@@ -274,6 +274,10 @@ __device__ __forceinline__ float lg2_approx(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Programmatic dependent launch: returns once the preceding kernel of the stream has completed and its
+// memory operations are visible (a no-op for a kernel launched without the attribute).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float sigmoid_fast(float x) {
   // 0.5 tanh(x / 2) + 0.5: one MUFU op (tanh.approx, abs. error ~5e-4, below bf16 resolution of the
   // gated values) instead of ex2 + rcp

@@ -45,6 +45,7 @@ __global__ void trimul_pack_weights_kernel(const float* __restrict__ p_in, const
                                            const float* __restrict__ p_out, const float* __restrict__ g_out,
                                            bf16* __restrict__ W5, bf16* __restrict__ W5T, bf16* __restrict__ Wz,
                                            bf16* __restrict__ WzT, int C) {
+  griddep_wait();
   const int n = 5 * C * C;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int row = i / C, col = i % C;
@@ -88,6 +89,7 @@ __global__ void __launch_bounds__(256) trimul_ln_fwd_kernel(const bf16* __restri
                                                             const float* __restrict__ beta, bf16* __restrict__ zln,
                                                             float* __restrict__ mean, float* __restrict__ rstd,
                                                             int64_t R) {
+  griddep_wait();
   using L = RowLanes<C>;
   constexpr int G = 4;  // row groups per warp, all loads issued before the first use
   const int lane = threadIdx.x & 31;
@@ -145,6 +147,7 @@ __global__ void __launch_bounds__(256, 2) trimul_xnorm_fwd_kernel(const bf16* __
                                                                   bf16* __restrict__ xln, float* __restrict__ mean,
                                                                   float* __restrict__ rstd, int64_t NN,
                                                                   int tiles_per_batch, int n_tiles) {
+  griddep_wait();
   constexpr int TR = 64;                    // pair rows per tile; warp w owns rows 8w .. 8w+7
   constexpr int IN_PITCH = TR * 2 + 16;     // bytes per channel row of the input tile (+16: conflict-free ldmatrix)
   constexpr int OUT_PITCH = C * 2 + 16;     // bytes per pair row of the staging tile
@@ -251,6 +254,7 @@ struct EpiProjGate {
     int64_t NN;
   };
   static constexpr bool kPaired = true;
+  static constexpr bool kStaged = false;
   static constexpr int kSmemPerWarp = 32 * 33 * 4;
   struct Pre {
     float mk;  // pair mask of this lane's row
@@ -306,6 +310,7 @@ struct EpiOutGate {
     int C;
   };
   static constexpr bool kPaired = false;
+  static constexpr bool kStaged = false;
   static constexpr int kSmemPerWarp = 2048;
   struct Pre {
     uint4 g[4];  // 32 gate logits of this lane's row
@@ -348,6 +353,7 @@ struct EpiGateSplitBwd {
     int64_t NN;
   };
   static constexpr bool kPaired = true;
+  static constexpr bool kStaged = true;
   static constexpr int kSmemPerWarp = 32 * 33 * 4;
   struct Pre {
     uint4 d[4];  // incoming gradient, channel-major: d[g] = 8 consecutive rows of channel 8*g + lane/4
@@ -370,12 +376,9 @@ struct EpiGateSplitBwd {
     }
     pre.mk = (m < sh.M) ? p.mask[m] : 0.f;
   }
-  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
-                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane,
-                                                const Pre& pre) {
-    const int which = n0 / (2 * p.C);  // 0: a, 1: b
-    // the prefetched channel-major block is transposed through smem so that afterwards lane = row
-    // holds its 32 channels
+  // The prefetched channel-major block is transposed through smem so that afterwards lane = row finds
+  // its 32 channels at wsm[lane * 33 ..].
+  __device__ static __forceinline__ void stage(const Pre& pre, float* wsm, int lane) {
     float* col = wsm + (8 * (lane & 3)) * 33 + (lane >> 2);
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -388,6 +391,11 @@ struct EpiGateSplitBwd {
       }
     }
     __syncwarp();
+  }
+  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
+                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane,
+                                                const Pre& pre) {
+    const int which = n0 / (2 * p.C);  // 0: a, 1: b
     const float mk = pre.mk;
     float o0[32], o1[32];
 #pragma unroll
@@ -422,6 +430,7 @@ __global__ void __launch_bounds__(256) trimul_out_gate_bwd_kernel(const bf16* __
                                                                   const bf16* __restrict__ out,
                                                                   const bf16* __restrict__ gate, bf16* __restrict__ d_y,
                                                                   bf16* __restrict__ d_proj5, int64_t R, int C) {
+  griddep_wait();
   const int64_t n8 = R * C / 8;
   const int per_row = C / 8;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
@@ -461,6 +470,7 @@ __global__ void __launch_bounds__(256, 2) trimul_xnorm_bwd_kernel(const bf16* __
                                                                   const float* __restrict__ rstd,
                                                                   bf16* __restrict__ dx_cm, float* __restrict__ partials,
                                                                   int64_t NN, int tiles_per_batch, int n_tiles) {
+  griddep_wait();
   constexpr int TR = 64;
   constexpr int IN_PITCH = TR * 2 + 16;
   constexpr int OUT_PITCH = C * 2 + 16;
@@ -608,6 +618,7 @@ __global__ void __launch_bounds__(256) trimul_ln_bwd_kernel(const bf16* __restri
                                                             const float* __restrict__ rstd, bf16* __restrict__ d_z,
                                                             float* __restrict__ partials, int64_t R,
                                                             int rows_per_block) {
+  griddep_wait();
   using L = RowLanes<C>;
   __shared__ float red[8][2][C];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -675,6 +686,7 @@ __global__ void __launch_bounds__(256) trimul_ln_bwd_kernel(const bf16* __restri
 __global__ void __launch_bounds__(1024) trimul_colsum_fold_kernel(const float* __restrict__ partials, int n_blocks,
                                                                  int width, float* __restrict__ out_a,
                                                                  float* __restrict__ out_b, int half) {
+  griddep_wait();
   __shared__ float red[32][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.x * 32 + lane;
@@ -701,6 +713,7 @@ struct WgradDst {
 };
 __global__ void __launch_bounds__(256) trimul_wgrad_fold_kernel(const float* __restrict__ part, int n_splits, int M,
                                                                 int C, WgradDst d) {
+  griddep_wait();
   // 32 output elements per CTA, 8 warps.  Warp g adds its contiguous range of splits in ascending
   // order (the loads of a batch of 8 splits are independent, so all are in flight before the first
   // add), then the 8 range sums are added in range order: a fixed summation tree, no atomics.
@@ -737,6 +750,7 @@ __global__ void __launch_bounds__(256) trimul_wgrad_fold_kernel(const float* __r
 // First level of the LayerNorm-gradient fold: out[s][j] = fixed-order sum of in[s*256 .. s*256+255][j].
 __global__ void __launch_bounds__(1024) trimul_colsum_stage_kernel(const float* __restrict__ in, int n_in, int width,
                                                                    float* __restrict__ out) {
+  griddep_wait();
   __shared__ float red[32][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.x * 32 + lane;
@@ -769,7 +783,7 @@ static int pack_weights(const float* p_in, const float* g_in, const float* p_out
   pk->W5T = base + 5 * C * C;
   pk->Wz = base + 10 * C * C;
   pk->WzT = base + 11 * C * C;
-  trimul_pack_weights_kernel<<<(5 * C * C + 255) / 256, 256, 0, stream>>>(p_in, g_in, p_out, g_out, pk->W5, pk->W5T,
+  launch_kernel(trimul_pack_weights_kernel, dim3((5 * C * C + 255) / 256), dim3(256), 0, stream, p_in, g_in, p_out, g_out, pk->W5, pk->W5T,
                                                                           pk->Wz, pk->WzT, C);
   TPF_LAUNCH_OK();
   return TPF_OK;
@@ -798,7 +812,7 @@ static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk
   if (stages & 1) {
     const int64_t warps = (R + 4 * L::RPW - 1) / (4 * L::RPW);
     const int64_t blocks = (warps + 7) / 8;
-    trimul_ln_fwd_kernel<C><<<(unsigned)blocks, 256, 0, stream>>>(z, gin, bin, zln, mean_in, rstd_in, R);
+    launch_kernel(trimul_ln_fwd_kernel<C>, dim3((unsigned)blocks), dim3(256), 0, stream, z, gin, bin, zln, mean_in, rstd_in, R);
     TPF_LAUNCH_OK();
     EpiProjGate::Params ep{a_cm, b_cm, gate, mask, C, NN};
     if ((rc = proj_gemm<C, EpiProjGate>(zln, pk.W5, R, 5 * C, ep, status, stream))) return rc;
@@ -817,7 +831,7 @@ static int trimul_fwd_t(const bf16* z, const float* mask, const TrimulPacked& pk
       constexpr int smem = 2 * C * (64 * 2 + 16) + 64 * (C * 2 + 16);
       static PerDeviceOnce once;  // per instantiation
       if ((rc = ensure_dynamic_smem(kern, smem, once))) return rc;
-      kern<<<grid, 256, smem, stream>>>(x_cm, gout, bout, xln, mean_out, rstd_out, NN, tiles, (int)(B * tiles));
+      launch_kernel(kern, dim3(grid), dim3(256), smem, stream, x_cm, gout, bout, xln, mean_out, rstd_out, NN, tiles, (int)(B * tiles));
     }
     TPF_LAUNCH_OK();
     using Cfg = GemmCfg<128, C, 128, false, 128, false, 4>;
@@ -906,7 +920,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
   {
     int blocks = (int)((R * C / 8 + 255) / 256);
     if (blocks > 16 * sm_count()) blocks = 16 * sm_count();
-    trimul_out_gate_bwd_kernel<<<blocks, 256, 0, stream>>>(d_out, out, gate, w.d_y, w.d_proj5, R, C);
+    launch_kernel(trimul_out_gate_bwd_kernel, dim3(blocks), dim3(256), 0, stream, d_out, out, gate, w.d_y, w.d_proj5, R, C);
     TPF_LAUNCH_OK();
   }
   // 2. d_xln = d_y Wz ; d_wz = d_y^T xln
@@ -923,7 +937,7 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
   {
     WgradDst d;
     for (int i = 0; i < 5; ++i) d.dst[i] = d_p_out;
-    trimul_wgrad_fold_kernel<<<(C * C + 31) / 32, 256, 0, stream>>>(w.part_wz, w.splits_wz, C, C, d);
+    launch_kernel(trimul_wgrad_fold_kernel, dim3((C * C + 31) / 32), dim3(256), 0, stream, w.part_wz, w.splits_wz, C, C, d);
     TPF_LAUNCH_OK();
   }
   // 3. output norm backward -> d_x (channel-major), d_gamma_out, d_beta_out
@@ -934,16 +948,16 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
       constexpr int smem = 2 * C * (64 * 2 + 16) + 2 * 64 * (C * 2 + 16);
       static PerDeviceOnce once;  // per instantiation
       if ((rc = ensure_dynamic_smem(kern, smem, once))) return rc;
-      kern<<<w.blocks_ln_out, 256, smem, stream>>>(w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out, NN,
+      launch_kernel(kern, dim3(w.blocks_ln_out), dim3(256), smem, stream, w.d_xln, x_cm, gout, mean_out, rstd_out, w.dx_cm, w.part_ln_out, NN,
                                                   tiles, (int)(B * tiles));
     }
     TPF_LAUNCH_OK();
     {
       const int lvl = (w.blocks_ln_out + 255) / 256;
-      trimul_colsum_stage_kernel<<<dim3((2 * C + 31) / 32, lvl), 1024, 0, stream>>>(w.part_ln_out, w.blocks_ln_out,
+      launch_kernel(trimul_colsum_stage_kernel, dim3(dim3((2 * C + 31) / 32, lvl)), dim3(1024), 0, stream, w.part_ln_out, w.blocks_ln_out,
                                                                                     2 * C, w.part_lvl2);
       TPF_LAUNCH_OK();
-      trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(w.part_lvl2, lvl, 2 * C, d_gout, d_bout, C);
+      launch_kernel(trimul_colsum_fold_kernel, dim3((2 * C + 31) / 32), dim3(1024), 0, stream, w.part_lvl2, lvl, 2 * C, d_gout, d_bout, C);
       TPF_LAUNCH_OK();
     }
   }
@@ -985,20 +999,20 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
     d.dst[2] = d_p_in + C * C;      // b_p
     d.dst[3] = d_g_in + C * C;      // b_g
     d.dst[4] = d_g_out;             // g
-    trimul_wgrad_fold_kernel<<<(5 * C * C + 31) / 32, 256, 0, stream>>>(w.part_w5, w.splits_w5, 5 * C, C, d);
+    launch_kernel(trimul_wgrad_fold_kernel, dim3((5 * C * C + 31) / 32), dim3(256), 0, stream, w.part_w5, w.splits_w5, 5 * C, C, d);
     TPF_LAUNCH_OK();
   }
   // 7. input norm backward
   {
-    trimul_ln_bwd_kernel<C><<<w.blocks_ln_in, 256, 0, stream>>>(d_zln, z, gin, mean_in, rstd_in, d_z, w.part_ln_in, R,
+    launch_kernel(trimul_ln_bwd_kernel<C>, dim3(w.blocks_ln_in), dim3(256), 0, stream, d_zln, z, gin, mean_in, rstd_in, d_z, w.part_ln_in, R,
                                                                 w.rows_per_block_in);
     TPF_LAUNCH_OK();
     {
       const int lvl = (w.blocks_ln_in + 255) / 256;
-      trimul_colsum_stage_kernel<<<dim3((2 * C + 31) / 32, lvl), 1024, 0, stream>>>(w.part_ln_in, w.blocks_ln_in,
+      launch_kernel(trimul_colsum_stage_kernel, dim3(dim3((2 * C + 31) / 32, lvl)), dim3(1024), 0, stream, w.part_ln_in, w.blocks_ln_in,
                                                                                     2 * C, w.part_lvl2);
       TPF_LAUNCH_OK();
-      trimul_colsum_fold_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(w.part_lvl2, lvl, 2 * C, d_gin, d_bin, C);
+      launch_kernel(trimul_colsum_fold_kernel, dim3((2 * C + 31) / 32), dim3(1024), 0, stream, w.part_lvl2, lvl, 2 * C, d_gin, d_bin, C);
       TPF_LAUNCH_OK();
     }
   }
