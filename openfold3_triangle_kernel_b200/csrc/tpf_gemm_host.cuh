@@ -43,6 +43,13 @@ int launch_gemm(const void* A, int64_t lda, int64_t bsa, const void* B, int64_t 
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid > tiles) grid = tiles;
   if (grid < 1) return TPF_OK;
+  if constexpr (Cfg::STAT != 0) {
+    const int k_len = sh.k_per_split > 0 ? sh.k_per_split : sh.K;
+    TPF_REQUIRE(k_len <= Cfg::STAT_KB * Cfg::BK, TPF_ERR_UNSUPPORTED,
+                "gemm: K = %d exceeds the stationary operand buffer (%d)", k_len, Cfg::STAT_KB * Cfg::BK);
+    const int per = (tiles + grid - 1) / grid;  // contiguous tiles per CTA; CTAs that would get none are not launched
+    grid = (tiles + per - 1) / per;
+  }
   launch_kernel(kern, dim3(grid), dim3(Cfg::THREADS), smem_bytes, stream, tmA, tmB, sh, ep, status);
   TPF_LAUNCH_OK();
   return TPF_OK;

@@ -62,6 +62,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe (try_wait may suspend the thread for a while when the phase is still open).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 
 // Per-CTA abort state: `flag` lives in shared memory, `status` in global memory.
 struct WaitCtx {
@@ -201,6 +213,71 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One k-block of UMMAs issued under two barrier probes.
+// A barrier probe (test_wait / try_wait) answers after 150+ cycles even when the phase completed long ago,
+// and the issuing thread's instruction stream is the critical path of the tensor pipe.  Here the probes of
+// the barriers needed NEXT (the next stage's `full`, the next tile's accumulator) are issued first, then the
+// four UMMAs of this k-block (descriptor j = base + j * STEP in the start-address field) and the commit that
+// releases the stage; the probe answers are read only after all of that has been issued.
+// Returns bit 0: probe_a done, bit 1: probe_b done.
+template <int A_STEP, int B_STEP>
+__device__ __forceinline__ uint32_t umma_ss_x4_probed(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                      uint32_t accumulate_first, uint64_t* commit_bar,
+                                                      uint64_t* probe_a, uint32_t parity_a, uint64_t* probe_b,
+                                                      uint32_t parity_b) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, qa, qb;\n\t.reg .b64 ad, bd;\n\t.reg .b32 ra, rb;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qa, [%7], %8;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qb, [%9], %10;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, p;\n\t"
+      "add.s64 ad, %2, %11;\n\t add.s64 bd, %3, %12;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], ad, bd, %4, 1;\n\t"
+      "add.s64 ad, ad, %11;\n\t add.s64 bd, bd, %12;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], ad, bd, %4, 1;\n\t"
+      "add.s64 ad, ad, %11;\n\t add.s64 bd, bd, %12;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], ad, bd, %4, 1;\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+      "selp.u32 ra, 1, 0, qa;\n\t selp.u32 rb, 2, 0, qb;\n\t or.b32 %0, ra, rb;\n\t}"
+      : "=r"(r)
+      : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first), "r"(smem_u32(commit_bar)),
+        "r"(smem_u32(probe_a)), "r"(parity_a), "r"(smem_u32(probe_b)), "r"(parity_b), "n"(A_STEP), "n"(B_STEP)
+      : "memory");
+  return r;
+}
+// The same for a k-block computed with the operand roles exchanged: UMMAs (w, x) -> d0 and (w + W1_OFF, x) -> d1.
+template <int STEP, int W1_OFF>
+__device__ __forceinline__ uint32_t umma_ss_x4x2_probed(uint32_t d0, uint32_t d1, uint64_t wdesc, uint64_t xdesc,
+                                                        uint32_t idesc, uint32_t accumulate_first, uint64_t* commit_bar,
+                                                        uint64_t* probe_a, uint32_t parity_a, uint64_t* probe_b,
+                                                        uint32_t parity_b) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, qa, qb;\n\t.reg .b64 wd, w1, xd;\n\t.reg .b32 ra, rb;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qa, [%8], %9;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qb, [%10], %11;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "add.s64 w1, %3, %13;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], %3, %4, %5, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], w1, %4, %5, p;\n\t"
+      "add.s64 wd, %3, %12;\n\t add.s64 w1, w1, %12;\n\t add.s64 xd, %4, %12;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], wd, xd, %5, 1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], w1, xd, %5, 1;\n\t"
+      "add.s64 wd, wd, %12;\n\t add.s64 w1, w1, %12;\n\t add.s64 xd, xd, %12;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], wd, xd, %5, 1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], w1, xd, %5, 1;\n\t"
+      "add.s64 wd, wd, %12;\n\t add.s64 w1, w1, %12;\n\t add.s64 xd, xd, %12;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], wd, xd, %5, 1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], w1, xd, %5, 1;\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+      "selp.u32 ra, 1, 0, qa;\n\t selp.u32 rb, 2, 0, qb;\n\t or.b32 %0, ra, rb;\n\t}"
+      : "=r"(r)
+      : "r"(d0), "r"(d1), "l"(wdesc), "l"(xdesc), "r"(idesc), "r"(accumulate_first), "r"(smem_u32(commit_bar)),
+        "r"(smem_u32(probe_a)), "r"(parity_a), "r"(smem_u32(probe_b)), "r"(parity_b), "n"(STEP), "n"(W1_OFF)
+      : "memory");
+  return r;
+}
 // Arrive on `bar` once every UMMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -278,6 +355,11 @@ __device__ __forceinline__ float lg2_approx(float x) {
 // memory operations are visible (a no-op for a kernel launched without the attribute).
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+__device__ __forceinline__ float tanh_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
 __device__ __forceinline__ float sigmoid_fast(float x) {
   // 0.5 tanh(x / 2) + 0.5: one MUFU op (tanh.approx, abs. error ~5e-4, below bf16 resolution of the
   // gated values) instead of ex2 + rcp

@@ -257,16 +257,57 @@ struct EpiProjGate {
   static constexpr bool kStaged = false;
   static constexpr int kSmemPerWarp = 32 * 33 * 4;
   struct Pre {
-    float mk;  // pair mask of this lane's row
+    float mk;  // pair mask: of this lane's row, or (exchanged tile) of row `lane` of the warp's 32-row chunk
   };
-  __device__ static __forceinline__ void prefetch2(const Params& p, const GemmShape& sh, int, int m, int, int, int,
-                                                   Pre& pre) {
+  // At C = 128 the a and b tiles are computed with the operand roles exchanged: accumulator lane = channel,
+  // accumulator column = pair row, so a lane holds 32 consecutive pair rows of ONE channel, which is 64
+  // contiguous bytes of the channel-major output, and no transpose is needed.  The gate tile (row-major
+  // output) keeps lane = pair row.
+  __device__ static __forceinline__ bool swapped(const Params& p, int n0) { return n0 < 4 * p.C; }
+  __device__ static __forceinline__ void prefetch2(const Params& p, const GemmShape& sh, int, int m0, int rit, int,
+                                                   int c0, int lane, bool swap, Pre& pre) {
+    const int m = swap ? m0 + c0 + lane : m0 + rit;
     pre.mk = (m < sh.M) ? p.mask[m] : 0.f;
   }
-  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
-                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane,
-                                                const Pre& pre) {
+  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m0, int rit, int n0,
+                                                int c0, const float (&v0)[32], const float (&v1)[32], float* wsm,
+                                                int lane, bool swap, const Pre& pre) {
     const int which = n0 / (2 * p.C);
+    if (swap) {
+      // lane = channel `rit`; v0[i] / v1[i] = projection / gate logit of pair row m0 + c0 + i
+      wsm[lane] = pre.mk;
+      __syncwarp();
+      const uint64_t half2 = f2_pack(0.5f, 0.5f);
+      uint32_t ow[16];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 mk = reinterpret_cast<const float4*>(wsm)[q];  // same address in every lane: one broadcast
+        const float mks[4] = {mk.x, mk.y, mk.z, mk.w};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int i = 4 * q + 2 * e;
+          float h0, h1, a0, a1;
+          f2_unpack(f2_mul(f2_pack(v1[i], v1[i + 1]), half2), h0, h1);
+          const uint64_t sg = f2_fma(f2_pack(tanh_fast(h0), tanh_fast(h1)), half2, half2);
+          const uint64_t pm = f2_mul(f2_pack(v0[i], v0[i + 1]), f2_pack(mks[2 * e], mks[2 * e + 1]));
+          f2_unpack(f2_mul(pm, sg), a0, a1);
+          ow[2 * q + e] = pack_bf16x2(a0, a1);
+        }
+      }
+      __syncwarp();  // the mask row has been read: the scratch becomes the staging tile
+      // Rows (and the sharded row count) are multiples of 64, so the 32-row chunk lies inside one batch entry
+      // and is inside M as a whole or not at all.  A lane's 64 bytes go out through the staging tile so that one
+      // store instruction covers 8 channels x 64 contiguous bytes instead of 32 channels x 16 bytes.
+      const int r0 = m0 + c0;
+      const int bb = (int)((uint32_t)r0 / (uint32_t)p.NN);
+      const int rr = r0 - bb * (int)p.NN;
+      bf16* blk = (which == 0 ? p.a_cm : p.b_cm) + ((int64_t)bb * p.C + (rit - lane)) * p.NN + rr;  // channel of lane 0
+      const bool ok = r0 < sh.M;
+      warp_tile_store(reinterpret_cast<uint8_t*>(wsm), lane, ow,
+                      [&](int r) -> bf16* { return ok ? blk + (int64_t)r * p.NN : nullptr; });
+      return;
+    }
+    const int m = m0 + rit;
     const int m_base = m - lane;  // first row of this warp's 32-row block (a multiple of 32)
     if (which == 2) {
       uint32_t pk[16];
@@ -278,14 +319,17 @@ struct EpiProjGate {
       });
       return;
     }
+    // a / b tile with lane = pair row (C < 128): each lane owns one row of the accumulator tile, which would
+    // make 2-byte scattered stores; the 32x32 block is transposed through a per-warp smem tile so that each
+    // lane writes 8 consecutive rows of four channels (4 x 16 bytes).
     const float mk = pre.mk;
 #pragma unroll
     for (int i = 0; i < 32; ++i) wsm[lane * 33 + i] = v0[i] * sigmoid_fast(v1[i]) * mk;
     __syncwarp();
     // four lanes per channel: each store instruction covers 8 channels x 64 contiguous bytes (32 rows)
-    const int64_t bb = m_base / p.NN, rr = m_base - bb * p.NN;
+    const int bb = (int)((uint32_t)m_base / (uint32_t)p.NN), rr = m_base - bb * (int)p.NN;
     const int piece = lane & 3;  // rows 8*piece .. 8*piece+7 of the block
-    bf16* dst = (which == 0 ? p.a_cm : p.b_cm) + (bb * p.C + c0 + (lane >> 2)) * p.NN + rr + 8 * piece;
+    bf16* dst = (which == 0 ? p.a_cm : p.b_cm) + ((int64_t)bb * p.C + c0 + (lane >> 2)) * p.NN + rr + 8 * piece;
     const float* col = wsm + (8 * piece) * 33 + (lane >> 2);
     const bool ok = m_base + 8 * piece + 7 < sh.M;
 #pragma unroll
@@ -359,15 +403,17 @@ struct EpiGateSplitBwd {
     uint4 d[4];  // incoming gradient, channel-major: d[g] = 8 consecutive rows of channel 8*g + lane/4
     float mk;    // pair mask of this lane's row
   };
-  __device__ static __forceinline__ void prefetch2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
-                                                   int lane, Pre& pre) {
+  __device__ static __forceinline__ bool swapped(const Params&, int) { return false; }
+  __device__ static __forceinline__ void prefetch2(const Params& p, const GemmShape& sh, int, int m0, int rit, int n0,
+                                                   int c0, int lane, bool, Pre& pre) {
     const int which = n0 / (2 * p.C);  // 0: a, 1: b
+    const int m = m0 + rit;
     const int m_base = m - lane;
-    const int64_t bb = m_base / p.NN, rr = m_base - bb * p.NN;
+    const int bb = (int)((uint32_t)m_base / (uint32_t)p.NN), rr = m_base - bb * (int)p.NN;
     // four lanes per channel: load g reads rows 8*piece..+7 of channel 8*g + lane/4, so one load
     // instruction covers 8 channels x 64 contiguous bytes
     const int piece = lane & 3;
-    const bf16* src = (which == 0 ? p.da_cm : p.db_cm) + (bb * p.C + c0 + (lane >> 2)) * p.NN + rr + 8 * piece;
+    const bf16* src = (which == 0 ? p.da_cm : p.db_cm) + ((int64_t)bb * p.C + c0 + (lane >> 2)) * p.NN + rr + 8 * piece;
     const bool ok = m_base + 8 * piece + 7 < sh.M;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -392,33 +438,39 @@ struct EpiGateSplitBwd {
     }
     __syncwarp();
   }
-  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m, int n0, int c0,
-                                                const float (&v0)[32], const float (&v1)[32], float* wsm, int lane,
-                                                const Pre& pre) {
+  __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m0, int rit, int n0,
+                                                int c0, const float (&v0)[32], const float (&v1)[32], float* wsm,
+                                                int lane, bool, const Pre& pre) {
     const int which = n0 / (2 * p.C);  // 0: a, 1: b
-    const float mk = pre.mk;
-    float o0[32], o1[32];
+    const int m = m0 + rit;
+    // d = incoming gradient * mask; t = tanh(g / 2): sigmoid s = 0.5 + 0.5 t, s (1 - s) = 0.25 - 0.25 t^2.
+    // Channel pairs (i, i + 1) go through packed fp32 arithmetic and are rounded to bf16 at once, so that
+    // only the packed results stay live.
+    const uint64_t mk2 = f2_pack(pre.mk, pre.mk);
+    const uint64_t half2 = f2_pack(0.5f, 0.5f), quarter2 = f2_pack(0.25f, 0.25f), nquarter2 = f2_pack(-0.25f, -0.25f);
+    uint32_t pk0[16], pk1[16];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float d = wsm[lane * 33 + i] * mk;
-      const float s = sigmoid_fast(v1[i]);
-      o0[i] = d * s;
-      o1[i] = d * v0[i] * s * (1.f - s);
+    for (int i = 0; i < 16; ++i) {
+      const uint64_t d2 = f2_mul(f2_pack(wsm[lane * 33 + 2 * i], wsm[lane * 33 + 2 * i + 1]), mk2);
+      float h0, h1, a0, a1, b0, b1;
+      f2_unpack(f2_mul(f2_pack(v1[2 * i], v1[2 * i + 1]), half2), h0, h1);
+      const uint64_t t2 = f2_pack(tanh_fast(h0), tanh_fast(h1));
+      const uint64_t s2 = f2_fma(t2, half2, half2);
+      const uint64_t ss2 = f2_fma(f2_mul(t2, nquarter2), t2, quarter2);
+      f2_unpack(f2_mul(d2, s2), a0, a1);
+      f2_unpack(f2_mul(f2_mul(d2, f2_pack(v0[2 * i], v0[2 * i + 1])), ss2), b0, b1);
+      pk0[i] = pack_bf16x2(a0, a1);
+      pk1[i] = pack_bf16x2(b0, b1);
     }
     __syncwarp();  // the transposed gradient block has been consumed: its smem is reused as staging tiles
     const int m_base = m - lane;
     bf16* dp = p.d_proj5 + which * 2 * p.C + c0;  // d_p block of row 0
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {         // 0: d_p, 1: d_g (C columns further)
-      uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i)
-        pk[i] = half ? pack_bf16x2(o1[2 * i], o1[2 * i + 1]) : pack_bf16x2(o0[2 * i], o0[2 * i + 1]);
-      bf16* blk = dp + half * p.C;
-      warp_tile_store(reinterpret_cast<uint8_t*>(wsm) + 2048 * half, lane, pk, [&](int r) -> bf16* {
-        return m_base + r < sh.M ? blk + (int64_t)(m_base + r) * 5 * p.C : nullptr;
-      });
-    }
+    warp_tile_store(reinterpret_cast<uint8_t*>(wsm), lane, pk0, [&](int r) -> bf16* {
+      return m_base + r < sh.M ? dp + (int64_t)(m_base + r) * 5 * p.C : nullptr;
+    });
+    warp_tile_store(reinterpret_cast<uint8_t*>(wsm) + 2048, lane, pk1, [&](int r) -> bf16* {
+      return m_base + r < sh.M ? dp + p.C + (int64_t)(m_base + r) * 5 * p.C : nullptr;  // d_g: C columns further
+    });
   }
 };
 
@@ -794,7 +846,10 @@ static int proj_gemm(const bf16* zln, const bf16* W5, int64_t R, int n_cols, con
                      int* status, cudaStream_t stream) {
   // The gated epilogues are latency-bound: at C = 128 (four 32-column chunk pairs per tile) 16
   // epilogue warps keep one chunk pair each in flight; narrower tiles have work for 8 only.
-  using Cfg = GemmCfg<128, 2 * C, 128, false, 128, false, (C == 128 ? 3 : 4), (C == 128 ? 16 : 8)>;
+  // The weight tile (2C rows x C) stays in shared memory while the CTA walks a contiguous range of row
+  // tiles; only the activations stream.  CTAs j, j + n/3, j + 2n/3 walk the same rows for the a, b and
+  // gate tiles at about the same time, so the activations come from DRAM once and from L2 twice.
+  using Cfg = GemmCfg<128, 2 * C, 128, false, 128, false, 4, (C == 128 ? 16 : 8), 2, (C + 63) / 64>;
   GemmShape sh{(int)R, n_cols, C, 1, 0};
   return launch_gemm<Cfg, Epi>(zln, C, 0, W5, C, 0, sh, ep, status, stream);
 }
@@ -983,7 +1038,8 @@ static int trimul_bwd_t(const bf16* d_out, const bf16* z, const float* mask, con
   // 6. d_zln = d_proj5 W5 ; dW5 = d_proj5^T zln
   bf16* d_zln = w.d_xln;
   {
-    using Cfg = GemmCfg<128, 128, 128, false, 128, false, 4>;
+    // d_proj5 streams from DRAM (W5^T comes from L2): six stages keep enough of it in flight per SM
+    using Cfg = GemmCfg<128, 128, 128, false, 128, false, 6>;
     using Epi = EpiStore<bf16>;
     GemmShape sh{(int)R, C, 5 * C, 1, 0};
     typename Epi::Params ep{d_zln, C, 0};
@@ -1122,3 +1178,4 @@ int trimul_bwd(const void* d_out, const void* z, const float* mask, const float*
 }
 
 }  // namespace tpf
+
