@@ -309,9 +309,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       wb = wa;
 
       auto issue_sdp = [&]() {  // S and dP of tile wa, then advance wa
-        if (wa.first_kk()) mbar_wait(&q_full[aq_s], aq_ph, wctx);
-        mbar_wait(&kv_full[akv_s], akv_ph, wctx);
-        mbar_wait(sdp_free, sdpfree_ph, wctx);
+        if (wa.first_kk()) mbar_wait3(&q_full[aq_s], aq_ph, &kv_full[akv_s], akv_ph, sdp_free, sdpfree_ph, wctx);
+        else mbar_wait2(&kv_full[akv_s], akv_ph, sdp_free, sdpfree_ph, wctx);
         sdpfree_ph ^= 1;
         tc_fence_after();
         const uint64_t qo = aq_s * kTile16, ko = akv_s * kTile16;
@@ -549,10 +548,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint64_t nlse2 = f2_pack(neg_lse2, neg_lse2);
       const uint64_t ndel2 = f2_pack(-delta, -delta);
 
-      mbar_wait(sdp_full, sdpfull_ph, wctx);
+      mbar_wait3(sdp_full, sdpfull_ph, &kv_full[kv_s], kv_ph, &b_full[b_s], b_ph, wctx);
       sdpfull_ph ^= 1;
-      mbar_wait(&kv_full[kv_s], kv_ph, wctx);
-      mbar_wait(&b_full[b_s], b_ph, wctx);
       tc_fence_after();
       const uint8_t* bias_row = smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE + half_off;
       const float* mask_row = reinterpret_cast<const float*>(smem + Cfg::OFF_MASK + kv_s * 512) + 32 * part;
@@ -804,8 +801,7 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       int s = 0, buf = 0;
       uint32_t ph = 0, free_ph[2] = {1, 1};
       for (int pl = pl0; pl < pl1; ++pl) {
-        mbar_wait(&full[s], ph, wctx);
-        mbar_wait(&sdp_free[buf], free_ph[buf], wctx);
+        mbar_wait2(&full[s], ph, &sdp_free[buf], free_ph[buf], wctx);
         free_ph[buf] ^= 1;
         tc_fence_after();
         const uint32_t st = smem_u32(smem + Cfg::OFF_ST + s * Cfg::STAGE);
@@ -891,9 +887,8 @@ attn_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       l_n1 = l_n2;
       dl_n1 = dl_n2;
       load_row_scalars(pl + 2, l_n2, dl_n2);
-      mbar_wait(&sdp_full[buf], full_ph[buf], wctx);
+      mbar_wait2(&sdp_full[buf], full_ph[buf], &full[s], ph, wctx);
       full_ph[buf] ^= 1;
-      mbar_wait(&full[s], ph, wctx);
       tc_fence_after();
       const float* mask_row =
           reinterpret_cast<const float*>(smem + Cfg::OFF_ST + s * Cfg::STAGE + 4 * Cfg::TILE) + CPT * part;

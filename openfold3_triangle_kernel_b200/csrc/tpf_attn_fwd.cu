@@ -222,8 +222,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
 
       auto issue_qk = [&](bool last) {
-        mbar_wait(&kv_full[k_s], k_ph, wctx);
-        mbar_wait(s_free, sfree_ph, wctx);  // the softmax warps have read the whole previous S tile
+        // s_free: the softmax warps have read the whole previous S tile
+        mbar_wait2(&kv_full[k_s], k_ph, s_free, sfree_ph, wctx);
         sfree_ph ^= 1;
         tc_fence_after();
         // descriptors differ from the hoisted ones only in the start-address field (bits 0-13, in 16-byte units)
@@ -255,9 +255,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             q_ph ^= 1;
             issue_qk(KT == 1);
           }
-          mbar_wait(p_ready, pready_ph, wctx);
+          mbar_wait2(p_ready, pready_ph, &kv_full[v_s], v_ph, wctx);
           pready_ph ^= 1;
-          mbar_wait(&kv_full[v_s], v_ph, wctx);
           tc_fence_after();
           const uint64_t vd = v_desc0 + (uint64_t)((v_s * Cfg::KV_TILE) >> 4);
 #pragma unroll
@@ -300,13 +299,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool tail = (j + 1) * KEYS > p.N;
         const float2 mprobe = *reinterpret_cast<const float2*>(mask_row + 2 * lane);
         const bool general = tail || __any_sync(0xffffffffu, (mprobe.x != 0.f) || (mprobe.y != 0.f));
-        mbar_wait(&b_full[b_s], b_ph, wctx);
         const uint8_t* bias_row = smem + Cfg::OFF_BIAS + b_s * Cfg::BIAS_STAGE + row * 128;
         if (j > 0) {
           // P V of the previous tile must be complete before P is overwritten or O is rescaled (it was
           // issued a whole tile ago)
-          mbar_wait(pv_done, pv_ph, wctx);
+          mbar_wait2(&b_full[b_s], b_ph, pv_done, pv_ph, wctx);
           pv_ph ^= 1;
+        } else {
+          mbar_wait(&b_full[b_s], b_ph, wctx);
         }
         tc_fence_after();
         float neg_m = (m_use == -INFINITY) ? 0.f : -m_use * kLog2e;

@@ -101,6 +101,44 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+// Waits on two / three barriers at once.  A probe answers only after 150+ cycles even when its phase
+// completed long ago; probes issued back to back overlap, sequential waits would pay that latency each.
+// The blocking waits are the fallback for the (rare) case that one of the phases is still open.
+__device__ __forceinline__ void mbar_wait2(uint64_t* a, uint32_t pa, uint64_t* b, uint32_t pb, const WaitCtx& ctx) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred qa, qb;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qa, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qb, [%3], %4;\n\t"
+      "and.pred qa, qa, qb;\n\t"
+      "selp.u32 %0, 1, 0, qa;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(a)), "r"(pa), "r"(smem_u32(b)), "r"(pb)
+      : "memory");
+  if (ok) return;
+  mbar_wait(a, pa, ctx);
+  mbar_wait(b, pb, ctx);
+}
+__device__ __forceinline__ void mbar_wait3(uint64_t* a, uint32_t pa, uint64_t* b, uint32_t pb, uint64_t* c, uint32_t pc,
+                                           const WaitCtx& ctx) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred qa, qb, qc;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qa, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qb, [%3], %4;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 qc, [%5], %6;\n\t"
+      "and.pred qa, qa, qb;\n\t"
+      "and.pred qa, qa, qc;\n\t"
+      "selp.u32 %0, 1, 0, qa;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(a)), "r"(pa), "r"(smem_u32(b)), "r"(pb), "r"(smem_u32(c)), "r"(pc)
+      : "memory");
+  if (ok) return;
+  mbar_wait(a, pa, ctx);
+  mbar_wait(b, pb, ctx);
+  mbar_wait(c, pc, ctx);
+}
+
 // ----------------------------------------------------------------------------
 // Proxy / tcgen05 fences
 // ----------------------------------------------------------------------------
