@@ -70,18 +70,25 @@ __global__ void trimul_pack_weights_kernel(const float* __restrict__ p_in, const
 // =============================================================================================
 // LayerNorm over the last dim of a row-major [R,C] bf16 tensor (input norm), forward
 // =============================================================================================
+// Row-wise LayerNorm kernels: a lane owns 8 consecutive channels (one 16-byte load), the lanes of a row
+// sit in a slot of LS lanes (a power of two; the lanes beyond C / 8 of a slot idle when C = 96), and a warp
+// works on 32 / LS rows at a time.
 template <int C>
 struct RowLanes {
-  static constexpr int LPR = C / 4;                 // lanes per row, 4 channels each
-  static constexpr int RPW = 32 / LPR;              // rows per warp (1 when C = 96)
-  static constexpr int RED = (C == 96) ? 32 : LPR;  // shuffle-reduction width
+  static constexpr int LPR = C / 8;                               // lanes that hold a row
+  static constexpr int LS = LPR <= 4 ? 4 : LPR <= 8 ? 8 : 16;     // lanes per row slot
+  static constexpr int RPW = 32 / LS;                             // rows per warp step
 };
 
 template <int C>
-__device__ __forceinline__ float group_sum(float v) {
+__device__ __forceinline__ float slot_sum(float v) {
 #pragma unroll
-  for (int off = RowLanes<C>::RED / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  for (int off = RowLanes<C>::LS / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
   return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&x)[8]) {
+  x[0] = bf16_lo(u.x); x[1] = bf16_hi(u.x); x[2] = bf16_lo(u.y); x[3] = bf16_hi(u.y);
+  x[4] = bf16_lo(u.z); x[5] = bf16_hi(u.z); x[6] = bf16_lo(u.w); x[7] = bf16_hi(u.w);
 }
 
 template <int C>
@@ -94,35 +101,46 @@ __global__ void __launch_bounds__(256) trimul_ln_fwd_kernel(const bf16* __restri
   constexpr int G = 4;  // row groups per warp, all loads issued before the first use
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int sub = lane / L::LPR, part = lane % L::LPR;
-  float4 g = make_float4(0.f, 0.f, 0.f, 0.f), b = g;
-  if (sub < L::RPW) {
-    g = *reinterpret_cast<const float4*>(gamma + part * 4);
-    b = *reinterpret_cast<const float4*>(beta + part * 4);
+  const int sub = lane / L::LS, part = lane % L::LS;
+  const bool on = part < L::LPR;
+  float g[8], b[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    g[e] = on ? gamma[part * 8 + e] : 0.f;
+    b[e] = on ? beta[part * 8 + e] : 0.f;
   }
-  uint2 u[G];
+  uint4 u[G];
   bool active[G];
 #pragma unroll
   for (int r = 0; r < G; ++r) {
     const int64_t row = (warp * G + r) * L::RPW + sub;
-    active[r] = sub < L::RPW && row < R;
-    u[r] = make_uint2(0u, 0u);
-    if (active[r]) u[r] = *reinterpret_cast<const uint2*>(z + row * C + part * 4);
+    active[r] = on && row < R;
+    u[r] = make_uint4(0u, 0u, 0u, 0u);
+    if (active[r]) u[r] = *reinterpret_cast<const uint4*>(z + row * C + part * 8);
   }
 #pragma unroll
   for (int r = 0; r < G; ++r) {
     const int64_t row = (warp * G + r) * L::RPW + sub;
-    const float x[4] = {bf16_lo(u[r].x), bf16_hi(u[r].x), bf16_lo(u[r].y), bf16_hi(u[r].y)};
-    const float s1 = group_sum<C>(x[0] + x[1] + x[2] + x[3]);
-    const float s2 = group_sum<C>(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+    float x[8];
+    unpack8(u[r], x);
+    float a1 = 0.f, a2 = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      a1 += x[e];
+      a2 += x[e] * x[e];
+    }
+    const float s1 = slot_sum<C>(a1);
+    const float s2 = slot_sum<C>(a2);
     const float mu = s1 * (1.f / C);
     const float var = fmaxf(s2 * (1.f / C) - mu * mu, 0.f);
     const float rs = rsqrtf(var + 1e-5f);
     if (active[r]) {
-      uint2 o;
-      o.x = pack_bf16x2((x[0] - mu) * rs * g.x + b.x, (x[1] - mu) * rs * g.y + b.y);
-      o.y = pack_bf16x2((x[2] - mu) * rs * g.z + b.z, (x[3] - mu) * rs * g.w + b.w);
-      *reinterpret_cast<uint2*>(zln + row * C + part * 4) = o;
+      uint4 o;
+      o.x = pack_bf16x2((x[0] - mu) * rs * g[0] + b[0], (x[1] - mu) * rs * g[1] + b[1]);
+      o.y = pack_bf16x2((x[2] - mu) * rs * g[2] + b[2], (x[3] - mu) * rs * g[3] + b[3]);
+      o.z = pack_bf16x2((x[4] - mu) * rs * g[4] + b[4], (x[5] - mu) * rs * g[5] + b[5]);
+      o.w = pack_bf16x2((x[6] - mu) * rs * g[6] + b[6], (x[7] - mu) * rs * g[7] + b[7]);
+      *reinterpret_cast<uint4*>(zln + row * C + part * 8) = o;
       if (part == 0) {
         mean[row] = mu;
         rstd[row] = rs;
@@ -674,54 +692,77 @@ __global__ void __launch_bounds__(256) trimul_ln_bwd_kernel(const bf16* __restri
   using L = RowLanes<C>;
   __shared__ float red[8][2][C];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int sub = lane / L::LPR, part = lane % L::LPR;
+  const int sub = lane / L::LS, part = lane % L::LS;
+  const bool on = part < L::LPR;
   const int64_t row_begin = (int64_t)blockIdx.x * rows_per_block;
-  float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (sub < L::RPW) g4 = *reinterpret_cast<const float4*>(gamma + part * 4);
-  float ag[4] = {0.f, 0.f, 0.f, 0.f}, ab[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-  for (int it = warp * L::RPW; it < rows_per_block; it += 8 * L::RPW) {
-    const int64_t row = row_begin + it + sub;
-    const bool active = sub < L::RPW && it + sub < rows_per_block && row < R;
-    float d[4] = {0.f, 0.f, 0.f, 0.f}, xh[4] = {0.f, 0.f, 0.f, 0.f};
-    float rs = 0.f;
-    if (active) {
-      const uint2 du = *reinterpret_cast<const uint2*>(d_zln + row * C + part * 4);
-      const uint2 zu = *reinterpret_cast<const uint2*>(z + row * C + part * 4);
-      const float mu = mean[row];
-      rs = rstd[row];
-      d[0] = bf16_lo(du.x); d[1] = bf16_hi(du.x); d[2] = bf16_lo(du.y); d[3] = bf16_hi(du.y);
-      xh[0] = (bf16_lo(zu.x) - mu) * rs; xh[1] = (bf16_hi(zu.x) - mu) * rs;
-      xh[2] = (bf16_lo(zu.y) - mu) * rs; xh[3] = (bf16_hi(zu.y) - mu) * rs;
-    }
-    const float gd[4] = {g4.x * d[0], g4.y * d[1], g4.z * d[2], g4.w * d[3]};
-    const float m1 = group_sum<C>(gd[0] + gd[1] + gd[2] + gd[3]) * (1.f / C);
-    const float m2 = group_sum<C>(gd[0] * xh[0] + gd[1] * xh[1] + gd[2] * xh[2] + gd[3] * xh[3]) * (1.f / C);
-    if (active) {
-      uint2 o;
-      o.x = pack_bf16x2(rs * (gd[0] - m1 - xh[0] * m2), rs * (gd[1] - m1 - xh[1] * m2));
-      o.y = pack_bf16x2(rs * (gd[2] - m1 - xh[2] * m2), rs * (gd[3] - m1 - xh[3] * m2));
-      *reinterpret_cast<uint2*>(d_z + row * C + part * 4) = o;
+  float g[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        ag[e] += d[e] * xh[e];
-        ab[e] += d[e];
+  for (int e = 0; e < 8; ++e) g[e] = on ? gamma[part * 8 + e] : 0.f;
+  float ag[8], ab[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ag[e] = ab[e] = 0.f;
+  constexpr int G = 4;  // row groups in flight per warp: all their loads are issued before the first use
+  for (int it0 = warp * L::RPW; it0 < rows_per_block; it0 += G * 8 * L::RPW) {
+    uint4 du[G], zu[G];
+    float mu[G], rs[G];
+    bool active[G];
+#pragma unroll
+    for (int r = 0; r < G; ++r) {
+      const int it = it0 + r * 8 * L::RPW;
+      const int64_t row = row_begin + it + sub;
+      active[r] = on && it + sub < rows_per_block && row < R;
+      du[r] = zu[r] = make_uint4(0u, 0u, 0u, 0u);
+      mu[r] = rs[r] = 0.f;
+      if (active[r]) {
+        du[r] = *reinterpret_cast<const uint4*>(d_zln + row * C + part * 8);
+        zu[r] = *reinterpret_cast<const uint4*>(z + row * C + part * 8);
+        mu[r] = mean[row];
+        rs[r] = rstd[row];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < G; ++r) {
+      const int64_t row = row_begin + it0 + r * 8 * L::RPW + sub;
+      float d[8], xh[8];
+      unpack8(du[r], d);
+      unpack8(zu[r], xh);
+      float gd[8], a1 = 0.f, a2 = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        xh[e] = active[r] ? (xh[e] - mu[r]) * rs[r] : 0.f;
+        gd[e] = g[e] * d[e];
+        a1 += gd[e];
+        a2 += gd[e] * xh[e];
+      }
+      const float m1 = slot_sum<C>(a1) * (1.f / C);
+      const float m2 = slot_sum<C>(a2) * (1.f / C);
+      if (active[r]) {
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          o[e] = pack_bf16x2(rs[r] * (gd[2 * e] - m1 - xh[2 * e] * m2), rs[r] * (gd[2 * e + 1] - m1 - xh[2 * e + 1] * m2));
+        *reinterpret_cast<uint4*>(d_z + row * C + part * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          ag[e] += d[e] * xh[e];
+          ab[e] += d[e];
+        }
       }
     }
   }
-  // fixed-order fold: rows of a warp that share channels (sub = 0..RPW-1), then the 8 warps
+  // fixed-order fold: the row slots of a warp (sub = 0 .. RPW-1), then the 8 warps
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
+  for (int e = 0; e < 8; ++e) {
     float vg = ag[e], vb = ab[e];
     for (int s = 1; s < L::RPW; ++s) {
-      const float og = __shfl_sync(0xffffffffu, ag[e], (lane % L::LPR) + s * L::LPR);
-      const float ob = __shfl_sync(0xffffffffu, ab[e], (lane % L::LPR) + s * L::LPR);
+      const float og = __shfl_sync(0xffffffffu, ag[e], part + s * L::LS);
+      const float ob = __shfl_sync(0xffffffffu, ab[e], part + s * L::LS);
       vg += og;
       vb += ob;
     }
-    if (sub == 0 && part * 4 + e < C) {
-      red[warp][0][part * 4 + e] = vg;
-      red[warp][1][part * 4 + e] = vb;
+    if (sub == 0 && on) {
+      red[warp][0][part * 8 + e] = vg;
+      red[warp][1][part * 8 + e] = vb;
     }
   }
   __syncthreads();
@@ -940,8 +981,8 @@ static void plan_bwd_workspace(int64_t B, int64_t NN, int64_t C, char* base, Tri
     const int64_t tiles = B * ((NN + 63) / 64);
     w->blocks_ln_out = (int)(tiles < 2 * sm_count() ? tiles : 2 * sm_count());
   }
-  w->rows_per_block_in = 256;
-  w->blocks_ln_in = (int)((R + 255) / 256);
+  w->rows_per_block_in = 128;
+  w->blocks_ln_in = (int)((R + 127) / 128);
   w->part_ln_out = reinterpret_cast<float*>(take((int64_t)w->blocks_ln_out * 2 * C * 4));
   w->part_ln_in = reinterpret_cast<float*>(take((int64_t)w->blocks_ln_in * 2 * C * 4));
   {
