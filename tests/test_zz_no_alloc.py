@@ -56,10 +56,14 @@ def test_static_scratch_matches_workspace_entry_twice_in_a_row(shape):
         ref, got = _grads(B, O, H, N, D), _grads(B, O, H, N, D)
         ws = torch.empty(need, device="cuda", dtype=torch.uint8)
         _call("tpf_attn_bwd", t, ref, shape, extra=(C.ptr(ws), need))
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]   # driver-level: a cudaMalloc inside the library would show here
         _call("tpf_attn_bwd_static_scratch", t, got, shape)
         assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
+        if seed == 4:   # second pass: every kernel has been loaded and launched before, nothing lazy is left
+            assert torch.cuda.mem_get_info()[0] >= free_before
         assert C.device_status() == 0
         for n in ("dq", "dk", "dv", "dbias", "delta"):
             # same kernels, same summation order: identical bits
