@@ -262,6 +262,20 @@ __global__ void __launch_bounds__(256, 2) trimul_xnorm_fwd_kernel(const bf16* __
 // a and b are stored channel-major.  Each lane owns one row of the accumulator tile, which would
 // make 2-byte scattered stores; the 32x32 block is transposed through a per-warp smem tile so
 // that each lane writes 32 consecutive rows of ONE channel (4 x 16 bytes).
+// Integer divisions by run-time values cost a lone epilogue warp 300-600 cycles each (a chain of conversions and
+// a reciprocal on the XU pipe), once per tile and on its critical path, so the epilogues avoid them: the tile
+// kind comes from comparisons, and the batch entry of a row is found by division only when there is more than one.
+__device__ __forceinline__ int tile_kind(int n0, int C) { return n0 >= 4 * C ? 2 : n0 >= 2 * C ? 1 : 0; }
+__device__ __forceinline__ void split_row(int row, int64_t NN, int M, int& bb, int& rr) {
+  if ((int64_t)M <= NN) {  // one batch entry
+    bb = 0;
+    rr = row;
+  } else {
+    bb = (int)((uint32_t)row / (uint32_t)NN);
+    rr = row - bb * (int)NN;
+  }
+}
+
 struct EpiProjGate {
   struct Params {
     bf16* a_cm;        // [B*C][NN]
@@ -290,7 +304,7 @@ struct EpiProjGate {
   __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m0, int rit, int n0,
                                                 int c0, const float (&v0)[32], const float (&v1)[32], float* wsm,
                                                 int lane, bool swap, const Pre& pre) {
-    const int which = n0 / (2 * p.C);
+    const int which = tile_kind(n0, p.C);
     if (swap) {
       // lane = channel `rit`; v0[i] / v1[i] = projection / gate logit of pair row m0 + c0 + i
       wsm[lane] = pre.mk;
@@ -317,8 +331,8 @@ struct EpiProjGate {
       // and is inside M as a whole or not at all.  A lane's 64 bytes go out through the staging tile so that one
       // store instruction covers 8 channels x 64 contiguous bytes instead of 32 channels x 16 bytes.
       const int r0 = m0 + c0;
-      const int bb = (int)((uint32_t)r0 / (uint32_t)p.NN);
-      const int rr = r0 - bb * (int)p.NN;
+      int bb, rr;
+      split_row(r0, p.NN, sh.M, bb, rr);
       bf16* blk = (which == 0 ? p.a_cm : p.b_cm) + ((int64_t)bb * p.C + (rit - lane)) * p.NN + rr;  // channel of lane 0
       const bool ok = r0 < sh.M;
       warp_tile_store(reinterpret_cast<uint8_t*>(wsm), lane, ow,
@@ -345,7 +359,8 @@ struct EpiProjGate {
     for (int i = 0; i < 32; ++i) wsm[lane * 33 + i] = v0[i] * sigmoid_fast(v1[i]) * mk;
     __syncwarp();
     // four lanes per channel: each store instruction covers 8 channels x 64 contiguous bytes (32 rows)
-    const int bb = (int)((uint32_t)m_base / (uint32_t)p.NN), rr = m_base - bb * (int)p.NN;
+    int bb, rr;
+    split_row(m_base, p.NN, sh.M, bb, rr);
     const int piece = lane & 3;  // rows 8*piece .. 8*piece+7 of the block
     bf16* dst = (which == 0 ? p.a_cm : p.b_cm) + ((int64_t)bb * p.C + c0 + (lane >> 2)) * p.NN + rr + 8 * piece;
     const float* col = wsm + (8 * piece) * 33 + (lane >> 2);
@@ -424,10 +439,11 @@ struct EpiGateSplitBwd {
   __device__ static __forceinline__ bool swapped(const Params&, int) { return false; }
   __device__ static __forceinline__ void prefetch2(const Params& p, const GemmShape& sh, int, int m0, int rit, int n0,
                                                    int c0, int lane, bool, Pre& pre) {
-    const int which = n0 / (2 * p.C);  // 0: a, 1: b
+    const int which = tile_kind(n0, p.C);  // 0: a, 1: b
     const int m = m0 + rit;
     const int m_base = m - lane;
-    const int bb = (int)((uint32_t)m_base / (uint32_t)p.NN), rr = m_base - bb * (int)p.NN;
+    int bb, rr;
+    split_row(m_base, p.NN, sh.M, bb, rr);
     // four lanes per channel: load g reads rows 8*piece..+7 of channel 8*g + lane/4, so one load
     // instruction covers 8 channels x 64 contiguous bytes
     const int piece = lane & 3;
@@ -459,7 +475,7 @@ struct EpiGateSplitBwd {
   __device__ static __forceinline__ void apply2(const Params& p, const GemmShape& sh, int, int m0, int rit, int n0,
                                                 int c0, const float (&v0)[32], const float (&v1)[32], float* wsm,
                                                 int lane, bool, const Pre& pre) {
-    const int which = n0 / (2 * p.C);  // 0: a, 1: b
+    const int which = tile_kind(n0, p.C);  // 0: a, 1: b
     const int m = m0 + rit;
     // d = incoming gradient * mask; t = tanh(g / 2): sigmoid s = 0.5 + 0.5 t, s (1 - s) = 0.25 - 0.25 t^2.
     // Channel pairs (i, i + 1) go through packed fp32 arithmetic and are rounded to bf16 at once, so that
