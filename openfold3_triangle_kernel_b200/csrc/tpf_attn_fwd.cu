@@ -146,14 +146,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   const int KT = p.k_tiles;
 
-  // item -> (b, h, qt, o); o fastest so that CTAs running at the same time read the same bias strip
-  auto decode = [&](int item, int& b, int& h, int& qt, int& o) {
-    o = item % p.O;
-    int r = item / p.O;
-    qt = r % p.q_tiles;
-    r /= p.q_tiles;
-    h = r % p.H;
-    b = r / p.H;
+  // item -> (b, h, qt, o); o fastest so that CTAs running at the same time read the same bias strip.
+  // The coordinates are a mixed-radix counter advanced by the grid size: the divisions happen once, not per
+  // item (an integer division by a run-time value costs a warp several hundred cycles on its critical path).
+  struct ItemWalk {
+    int o, qt, h, b;      // current item
+    int so, sq, sh, sb;   // the step, decomposed
+    int O, Q, H;
+    __device__ void init(int item, int step, int O_, int Q_, int H_) {
+      O = O_; Q = Q_; H = H_;
+      o = item % O; int r = item / O;
+      qt = r % Q; r /= Q;
+      h = r % H; b = r / H;
+      so = step % O; r = step / O;
+      sq = r % Q; r /= Q;
+      sh = r % H; sb = r / H;
+    }
+    __device__ __forceinline__ void next() {
+      o += so;
+      int c = o >= O ? 1 : 0;
+      o -= c * O;
+      qt += sq + c;
+      c = qt >= Q ? 1 : 0;
+      qt -= c * Q;
+      h += sh + c;
+      c = h >= H ? 1 : 0;
+      h -= c * H;
+      b += sb + c;
+    }
   };
 
   if (warp == Cfg::WARP_TMA) {
@@ -165,9 +185,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t q_ph = 1;
       int kv_s = 0, b_s = 0, m_s = 0;
       uint32_t kv_ph = 1, b_ph = 1;
-      for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
-        int b, h, qt, o;
-        decode(item, b, h, qt, o);
+      ItemWalk iw;
+      iw.init(blockIdx.x, gridDim.x, p.O, p.q_tiles, p.H);
+      for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, iw.next()) {
+        const int b = iw.b, h = iw.h, qt = iw.qt, o = iw.o;
         const int bb = p.bias_broadcast ? 0 : b;
         mbar_wait(q_empty, q_ph, wctx);
         q_ph ^= 1;
@@ -284,9 +305,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t sfull_ph = 0, pv_ph = 0, b_ph = 0;
     int b_s = 0, m_s = 0;
 
-    for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
-      int b, h, qt, o;
-      decode(item, b, h, qt, o);
+    ItemWalk iw;
+    iw.init(blockIdx.x, gridDim.x, p.O, p.q_tiles, p.H);
+    for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, iw.next()) {
+      const int b = iw.b, h = iw.h, qt = iw.qt, o = iw.o;
       float m_use = -INFINITY, l_run = 0.f;
 
       for (int j = 0; j < KT; ++j) {
